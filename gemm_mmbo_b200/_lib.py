@@ -1,0 +1,55 @@
+"""ctypes binding of libmmbo_gemm.so (declarations: include/mmbo_gemm.h).
+
+There is no fallback of any kind: if the CUDA library has not been built, importing
+this module raises.  Build it with `python -m gemm_mmbo_b200.build`.
+"""
+from __future__ import annotations
+
+import ctypes
+import pathlib
+
+_PKG = pathlib.Path(__file__).resolve().parent
+LIB_PATH = _PKG / "_build" / "libmmbo_gemm.so"
+
+_sz = ctypes.c_size_t
+_vp = ctypes.c_void_p
+_fp = ctypes.POINTER(ctypes.c_float)
+_u32p = ctypes.POINTER(ctypes.c_uint32)
+_szp = ctypes.POINTER(ctypes.c_size_t)
+
+# name -> (restype, argtypes); every symbol declared in include/mmbo_gemm.h
+SIGNATURES = {
+    "mmbo_gemm_f32": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
+                                     _fp, _vp, _sz, ctypes.c_int, _vp]),
+    "mmbo_gemm_f16": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
+                                     _fp, _vp, _sz, ctypes.c_int, _vp]),
+    "mmbo_num_kernels": (ctypes.c_int, [ctypes.c_int]),
+    "mmbo_kernel_name": (ctypes.c_char_p, [ctypes.c_int, ctypes.c_int]),
+    "mmbo_kernel_params": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]),
+    "mmbo_select_kernel": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _vp, _sz,
+                                          _vp, _sz, _vp, _sz]),
+    "mmbo_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "mmbo_wgm_map": (None, [ctypes.c_uint32] * 5 + [_u32p, _u32p]),
+    "mmbo_shard_columns": (ctypes.c_int, [_sz, ctypes.c_int, ctypes.c_int, _sz, _szp, _szp]),
+    "mmbo_fill_f32": (ctypes.c_int, [_vp, _sz, _sz, _sz, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int,
+                                     ctypes.c_float, _sz, _sz, _sz, _vp]),
+    "mmbo_fill_f16": (ctypes.c_int, [_vp, _sz, _sz, _sz, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int,
+                                     ctypes.c_float, _sz, _sz, _sz, _vp]),
+    "mmbo_device_status": (ctypes.c_int, [_u32p]),
+}
+
+
+def load() -> ctypes.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built "
+            "(run `python -m gemm_mmbo_b200.build`). There is no CPU fallback.")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+LIB = load()

@@ -1,0 +1,334 @@
+// HGEMM (fp16 in, fp32 accumulate, fp16 out) on the sm_100a tensor cores:
+//   C = alpha * op(A) * op(B) + beta * C      (column-major, BLAS op() convention)
+//
+// This is the B200 counterpart of the reference's device kernels (general path:
+// src/gemm/ref/Kernels.cpp:153-1123; hand-tuned path:
+// src/gemm/assembly/naive_gemm_kernel_MT096x096x08_TT06_06_STT02_06_WG16_16_01_HALF_A_HALF_B.s),
+// redesigned around tcgen05:
+//
+//   * The kernel computes the transposed tile  D[n][m] = sum_l op(B)(l,n) * op(A)(m,l):
+//     the UMMA "M" axis (128 tensor-memory lanes) runs along the problem's N and the
+//     UMMA "N" axis (TM tensor-memory columns) runs along the problem's M, which is the
+//     contiguous axis of column-major C.  An epilogue thread therefore owns one column
+//     of C and TM consecutive rows of it, and packs 8 fp16 per 16-byte access.
+//   * No operand is ever transposed in memory: NN/NT/TN/TT only change which tensor
+//     map describes an operand and whether its shared-memory tile is "K-major"
+//     (contraction index contiguous: transA = T, transB = N) or "MN-major".
+//   * Roles (192 threads): warp 0 = TMA producer (one elected lane), warp 1 = tensor
+//     memory owner + UMMA issuer (one lane), warps 2-5 = epilogue, one per 32-lane
+//     quarter of tensor memory.
+//   * STAGES-deep ring of 128-byte-swizzled shared-memory tiles fed by TMA; two
+//     accumulators in tensor memory so the epilogue of tile i overlaps the main loop
+//     of tile i+1 (the idea sketched by the reference's two-tiles-per-work-group kernel,
+//     ..._HALF_A_HALF_B_ver3.s:931-962); persistent CTAs walk tiles in the reference's
+//     work-group-mapping order (raster.h).
+//   * Epilogue: tcgen05.ld -> alpha*acc (+ beta*C, with C fetched by TMA into the same
+//     staging buffer; beta == 0 never reads C, src/gemm/ref/Kernels.cpp:87) -> fp16 ->
+//     swizzled staging -> TMA store, per warp, double buffered.
+//   * Ragged M, N, K need no special code: TMA zero-fills out-of-range loads and clips
+//     out-of-range stores.
+//
+// Requirements checked by the host before choosing this kernel: 16-byte aligned base
+// pointers and leading dimensions that are multiples of 8 elements (TMA strides).
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+#include "raster.h"
+
+namespace mmbo {
+
+constexpr int kTileN = 128;  // problem-N extent of a CTA tile = UMMA M
+constexpr int kBlockK = 64;  // fp16 elements per stage along K = one 128-byte swizzle row
+constexpr int kUmmaK = 16;   // K extent of one kind::f16 UMMA
+constexpr int kEpiWarps = 4;
+constexpr int kEpiBufBytes = 32 * 128;  // 32 C columns x 64 rows of fp16, per warp buffer
+constexpr int kHgemmThreads = 192;
+
+template <int TM, int STAGES>
+struct HgemmSmem {
+  static constexpr int kBopBytes = kTileN * kBlockK * 2;  // op(B) tile  (UMMA A operand)
+  static constexpr int kAopBytes = TM * kBlockK * 2;      // op(A) tile  (UMMA B operand)
+  static constexpr int kStageBytes = kBopBytes + kAopBytes;
+  static constexpr int kEpiOffset = STAGES * kStageBytes;
+  static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiBufBytes;
+  static constexpr int kBarOffset = kEpiOffset + kEpiBytes;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], cload[4][2]
+  static constexpr int kNumBars = 2 * STAGES + 4 + 2 * kEpiWarps;
+  static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
+  static constexpr int kTotal = kMiscOffset + 16;
+  static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024 bytes
+};
+
+struct HgemmParams {
+  uint32_t m, n, k;
+  uint32_t tiles_m, tiles_n;  // ceil(m / TM), ceil(n / 128)
+  uint32_t wgm;               // work-group-mapping width (tile columns per block)
+  float alpha, beta;
+};
+
+template <int TM, int STAGES, bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(kHgemmThreads, 1)
+hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                     const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ CUtensorMap tmap_c, const HgemmParams p) {
+  using L = HgemmSmem<TM, STAGES>;
+  static_assert(TM == 128 || TM == 256, "TM is the UMMA N extent");
+  constexpr uint32_t kTmemCols = 2 * TM;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+  auto tmem_full_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tmem_empty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  auto cload_bar = [&](uint32_t w, uint32_t b) { return bar_base + 8u * (2 * STAGES + 4 + 2 * w + b); };
+  volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOffset);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOffset + 4);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t num_tiles = p.tiles_m * p.tiles_n;
+  const uint32_t num_kb = (p.k + kBlockK - 1) / kBlockK;
+
+  // ------------------------------------------------------------------ set-up --------
+  if (threadIdx.x == 0) {
+    *abort_flag = 0u;
+    for (uint32_t s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), kEpiWarps);
+    }
+    for (uint32_t w = 0; w < kEpiWarps; ++w)
+      for (uint32_t b = 0; b < 2; ++b) mbar_init(cload_bar(w, b), 1);
+    fence_mbar_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+    prefetch_tensormap(&tmap_c);
+  }
+  __syncwarp();
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  // ------------------------------------------------------------------ roles ---------
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, issued = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        uint32_t tm_idx, tn_idx;
+        mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
+        const int32_t m0 = static_cast<int32_t>(tm_idx * TM);
+        const int32_t n0 = static_cast<int32_t>(tn_idx * kTileN);
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kFaultWaitEmpty, stage)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = full_bar(stage);
+          const uint32_t s_bop = smem_base + stage * L::kStageBytes;
+          const uint32_t s_aop = s_bop + L::kBopBytes;
+          const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
+          mbar_expect_tx(bar, L::kStageBytes);
+          if constexpr (B_KMAJOR) {
+            tma_load_2d(s_bop, &tmap_b, bar, k0, n0);  // box {64 k, 128 n}
+          } else {
+#pragma unroll
+            for (int c = 0; c < kTileN / 64; ++c)  // boxes {64 n, 64 k}
+              tma_load_2d(s_bop + c * 8192, &tmap_b, bar, n0 + 64 * c, k0);
+          }
+          if constexpr (A_KMAJOR) {
+            tma_load_2d(s_aop, &tmap_a, bar, k0, m0);  // box {64 k, TM m}
+          } else {
+#pragma unroll
+            for (int c = 0; c < TM / 64; ++c)  // boxes {64 m, 64 k}
+              tma_load_2d(s_aop + c * 8192, &tmap_a, bar, m0 + 64 * c, k0);
+          }
+          ++issued;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Unwind: let every copy this thread issued land before the CTA's shared
+        // memory is released.  A stage already consumed reports complete at once.
+        uint32_t s = stage, ph = phase;
+        const uint32_t back = issued < STAGES ? issued : STAGES;
+        for (uint32_t i = 0; i < back; ++i) {
+          if (s == 0) {
+            s = STAGES;
+            ph ^= 1u;
+          }
+          --s;
+          uint32_t none = 0;
+          mbar_wait(full_bar(s), ph, &none, kFaultWaitFull, 0x100u + s, MMBO_DRAIN_LIMIT_NS);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===== UMMA issuer =====
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(0u, B_KMAJOR ? 0u : 1u, A_KMAJOR ? 0u : 1u, kTileN, TM);
+      constexpr uint32_t kStepBop = B_KMAJOR ? 32u : 2048u;  // bytes per UMMA K step
+      constexpr uint32_t kStepAop = A_KMAJOR ? 32u : 2048u;
+      constexpr uint32_t kLboBop = B_KMAJOR ? 16u : 8192u;
+      constexpr uint32_t kLboAop = A_KMAJOR ? 16u : 8192u;
+      uint32_t stage = 0, phase = 0, local_tile = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+        const uint32_t acc = local_tile & 1u;
+        const uint32_t acc_phase = (local_tile >> 1) & 1u;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, kFaultWaitTmemEmpty, acc)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * TM;
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, kFaultWaitFull, stage)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t s_bop = smem_base + stage * L::kStageBytes;
+          const uint32_t s_aop = s_bop + L::kBopBytes;
+          const uint64_t desc_a = make_smem_desc_sw128(s_bop, kLboBop, 1024u);
+          const uint64_t desc_b = make_smem_desc_sw128(s_aop, kLboAop, 1024u);
+#pragma unroll
+          for (uint32_t j = 0; j < kBlockK / kUmmaK; ++j) {
+            umma_ss<1, false>(d_tmem, desc_a + ((j * kStepBop) >> 4), desc_b + ((j * kStepAop) >> 4),
+                              idesc, (kb | j) != 0u ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // frees the stage once these UMMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(tmem_full_bar(acc));  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ===== epilogue: warp owns tensor-memory lanes [32q, 32q+32) = 32 columns of C =====
+    const uint32_t q = warp & 3u;
+    const uint32_t epi_w = warp - 2u;
+    const uint32_t buf_base = smem_base + L::kEpiOffset + epi_w * 2u * kEpiBufBytes;
+    uint8_t* buf_gen = smem_gen + L::kEpiOffset + epi_w * 2u * kEpiBufBytes;
+    const bool use_c = (p.beta != 0.0f);
+    const float alpha = p.alpha, beta = p.beta;
+    uint32_t local_tile = 0, chunk_ctr = 0;
+    uint32_t cphase[2] = {0u, 0u};
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+      uint32_t tm_idx, tn_idx;
+      mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
+      const uint32_t m0 = tm_idx * TM;
+      const uint32_t ncol0 = tn_idx * kTileN + 32u * q;  // first C column of this warp
+      const uint32_t acc = local_tile & 1u;
+      const uint32_t acc_phase = (local_tile >> 1) & 1u;
+      // Every lane polls; the verdict is made warp-uniform so that the aligned
+      // tcgen05 instructions below always run with a converged warp.
+      ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag,
+                                             kFaultWaitTmemFull, acc));
+      if (!ok) break;
+      tcgen05_fence_after();
+      const uint32_t t_warp = tmem_base + ((32u * q) << 16) + acc * TM;
+#pragma unroll 1
+      for (uint32_t c = 0; c < TM / 64; ++c, ++chunk_ctr) {
+        const uint32_t b = chunk_ctr & 1u;
+        const uint32_t sbuf = buf_base + b * kEpiBufBytes;
+        uint8_t* gbuf = buf_gen + b * kEpiBufBytes;
+        const uint32_t mrow0 = m0 + 64u * c;
+        const bool in_range = (mrow0 < p.m) && (ncol0 < p.n);  // warp-uniform
+        // The store issued from this buffer two chunks ago must have read it.
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        const bool load_c = use_c && in_range;
+        if (load_c && lane == 0) {
+          mbar_expect_tx(cload_bar(epi_w, b), kEpiBufBytes);
+          tma_load_2d(sbuf, &tmap_c, cload_bar(epi_w, b), static_cast<int32_t>(mrow0),
+                      static_cast<int32_t>(ncol0));
+        }
+        uint32_t r[32];
+        tmem_ld_32x32(t_warp + 64u * c, r);
+        if (load_c) {
+          if (!mbar_wait(cload_bar(epi_w, b), cphase[b], abort_flag, kFaultWaitCLoad, epi_w)) ok = false;
+          cphase[b] ^= 1u;
+        }
+        // `ok` may differ between lanes only after a time-out, when the data is
+        // discarded anyway; keep the warp converged for the aligned tcgen05 ops.
+#pragma unroll
+        for (uint32_t h = 0; h < 2; ++h) {
+          if (h == 1) tmem_ld_32x32(t_warp + 64u * c + 32u, r);
+          tmem_ld_wait();
+          if (h == 1 && c == TM / 64 - 1) {
+            // Accumulator fully read: hand it back to the UMMA issuer.
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+          }
+#pragma unroll
+          for (uint32_t jj = 0; jj < 4; ++jj) {
+            const uint32_t j = 4u * h + jj;  // 16-byte chunk of the 128-byte row
+            uint8_t* addr = gbuf + lane * 128u + ((j ^ (lane & 7u)) << 4);
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = alpha * __uint_as_float(r[8 * jj + e]);
+            if (load_c) {
+              const uint4 old = *reinterpret_cast<const uint4*>(addr);
+              const __half2* oh = reinterpret_cast<const __half2*>(&old);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(oh[e]);
+                v[2 * e] = fmaf(beta, f.x, v[2 * e]);
+                v[2 * e + 1] = fmaf(beta, f.y, v[2 * e + 1]);
+              }
+            }
+            uint4 out;
+            __half2* ph = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ph[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+            *reinterpret_cast<uint4*>(addr) = out;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (in_range && ok)
+            tma_store_2d(&tmap_c, sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
+          tma_store_commit();
+        }
+        ok = __all_sync(0xffffffffu, ok);
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown ------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace mmbo

@@ -1,0 +1,465 @@
+// C ABI of libmmbo_gemm.so: argument validation, kernel table, kernel selection, tensor
+// map construction and launches.  Counterpart of the reference's launch surface
+// (src/gemm/gemm.h:4-97 packs arguments and picks a table row; src/gemm/driver.h:15-61
+// loads a code object and launches it).  Unlike the reference nothing is loaded per
+// call: every kernel is linked into this library.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "../../include/mmbo_gemm.h"
+#include "hgemm_tcgen05.cuh"
+#include "ref_kernels.cuh"
+#include "sgemm_ffma.cuh"
+
+namespace mmbo {
+
+// ------------------------------------------------------------------ kernel table -----
+struct KernelRow {
+  const char* name;
+  int mt0, mt1, threads, depth_u, stages, cta_group, wgm, tensor;
+};
+
+// fp32 rows.  Names follow the reference's scheme (src/gemm/constants.h:20-33):
+// MT<tile m>x<tile n>x<DepthU>_TT<thread tile>_WG<threads>.
+static const KernelRow kF32Rows[] = {
+    {"sgemm_simple_MT032x008x01_TT01_01_WG256", 32, 8, 256, 1, 1, 1, 1, 0},
+    {"sgemm_ffma_MT128x128x16_TT08_08_WG256_WGM08", 128, 128, 256, 16, 2, 1, 8, 0},
+    {"sgemm_ffma_MT064x064x16_TT04_04_WG256_WGM08", 64, 64, 256, 16, 2, 1, 8, 0},
+};
+// fp16 rows: MT<tile m>x<tile n>x<DepthU>_S<stages>_CG<cta group>.
+static const KernelRow kF16Rows[] = {
+    {"hgemm_simple_MT032x008x01_TT01_01_WG256", 32, 8, 256, 1, 1, 1, 1, 0},
+    {"hgemm_tcgen05_MT256x128x64_S4_CG1_WG192_WGM08", 256, 128, 192, 64, 4, 1, 8, 1},
+    {"hgemm_tcgen05_MT128x128x64_S6_CG1_WG192_WGM08", 128, 128, 192, 64, 6, 1, 8, 1},
+};
+constexpr int kNumF32 = sizeof(kF32Rows) / sizeof(KernelRow);
+constexpr int kNumF16 = sizeof(kF16Rows) / sizeof(KernelRow);
+
+static const KernelRow* rows_of(int dtype, int* count) {
+  if (dtype == MMBO_DTYPE_F32) {
+    *count = kNumF32;
+    return kF32Rows;
+  }
+  if (dtype == MMBO_DTYPE_F16) {
+    *count = kNumF16;
+    return kF16Rows;
+  }
+  *count = 0;
+  return nullptr;
+}
+
+// ------------------------------------------------------------------ device info ------
+constexpr int kMaxDevices = 64;
+static int g_sm_count[kMaxDevices];
+
+static int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev;
+}
+
+static int sm_count() {
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return 148;
+  if (g_sm_count[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+      cudaGetLastError();
+      v = 148;
+    }
+    g_sm_count[dev] = v;
+  }
+  return g_sm_count[dev];
+}
+
+static uint32_t env_u32(const char* name, uint32_t fallback) {
+  const char* s = getenv(name);
+  if (!s || !*s) return fallback;
+  return (uint32_t)strtoul(s, nullptr, 10);
+}
+
+// ------------------------------------------------------------------ validation -------
+struct GemmArgs {
+  int transA, transB;
+  size_t m, n, k;
+  const void *A, *B;
+  void* C;
+  size_t lda, ldb, ldc;
+  float alpha, beta;
+};
+
+static int validate(const GemmArgs& g, const float* alpha, const float* beta) {
+  if ((g.transA != 0 && g.transA != 1) || (g.transB != 0 && g.transB != 1)) return MMBO_ERR_BAD_TRANS;
+  const size_t lim = 0x7fffffffull;
+  if (g.m > lim || g.n > lim || g.k > lim) return MMBO_ERR_BAD_DIM;
+  if (!alpha || !beta) return MMBO_ERR_NULL_POINTER;
+  if (g.m == 0 || g.n == 0) return MMBO_OK;
+  if (!g.C) return MMBO_ERR_NULL_POINTER;
+  if (g.ldc < g.m || g.ldc > lim) return MMBO_ERR_BAD_LDC;
+  if (g.k != 0) {
+    if (!g.A || !g.B) return MMBO_ERR_NULL_POINTER;
+    if (g.lda < (g.transA ? g.k : g.m) || g.lda > lim) return MMBO_ERR_BAD_LDA;
+    if (g.ldb < (g.transB ? g.n : g.k) || g.ldb > lim) return MMBO_ERR_BAD_LDB;
+  }
+  return MMBO_OK;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ------------------------------------------------------------------ TMA maps ---------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+static bool g_encode_tried = false;
+
+static EncodeTiledFn encode_fn() {
+  if (!g_encode_tried) {
+    g_encode_tried = true;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    else
+      cudaGetLastError();
+  }
+  return g_encode;
+}
+
+// 2-D map over a column-major array: dimension 0 (contiguous) has `inner` elements,
+// dimension 1 has `outer` elements `ld` elements apart.  128-byte swizzle; out-of-range
+// elements read as zero.
+static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem_bytes, const void* base,
+                       size_t inner, size_t outer, size_t ld, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return MMBO_ERR_NO_DRIVER_ENTRY;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * elem_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MMBO_OK : MMBO_ERR_TENSOR_MAP;
+}
+
+// ------------------------------------------------------------------ launches ---------
+template <typename T>
+static int launch_simple(const GemmArgs& g, cudaStream_t st) {
+  const size_t gx = (g.m + 31) / 32, gy = (g.n + 7) / 8;
+  if (gy > 65535 || gx > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
+  dim3 grid((unsigned)gx, (unsigned)gy), block(32, 8);
+  gemm_simple_kernel<T><<<grid, block, 0, st>>>(g.transA, g.transB, g.m, g.n, g.k, g.alpha,
+                                                static_cast<const T*>(g.A), g.lda,
+                                                static_cast<const T*>(g.B), g.ldb, g.beta,
+                                                static_cast<T*>(g.C), g.ldc);
+  return (int)cudaGetLastError();
+}
+
+template <typename T>
+static int launch_scale(const GemmArgs& g, cudaStream_t st) {
+  const size_t gx = (g.m + 31) / 32, gy = (g.n + 7) / 8;
+  if (gy > 65535 || gx > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
+  dim3 grid((unsigned)gx, (unsigned)gy), block(32, 8);
+  scale_c_kernel<T><<<grid, block, 0, st>>>(g.m, g.n, g.beta, static_cast<T*>(g.C), g.ldc);
+  return (int)cudaGetLastError();
+}
+
+template <int BM, int BN, int TTM, int TTN>
+static int launch_sgemm_ffma(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
+  constexpr int BK = 16;
+  SgemmParams p;
+  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
+  p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
+  p.alpha = g.alpha; p.beta = g.beta; p.wgm = wgm;
+  // 128-bit accesses: base and pitch 16-byte aligned, and the contiguous extent a
+  // multiple of 4 so that no vector straddles the matrix edge.
+  const size_t a_contig = g.transA ? g.k : g.m, b_contig = g.transB ? g.n : g.k;
+  p.vec_a = aligned16(g.A) && g.lda % 4 == 0 && a_contig % 4 == 0;
+  p.vec_b = aligned16(g.B) && g.ldb % 4 == 0 && b_contig % 4 == 0;
+  p.vec_c = aligned16(g.C) && g.ldc % 4 == 0;
+  const size_t gx = (g.m + BM - 1) / BM, gy = (g.n + BN - 1) / BN;
+  if (gy > 65535) return MMBO_ERR_TOO_LARGE;
+  dim3 grid((unsigned)gx, (unsigned)gy), block((BM / TTM) * (BN / TTN));
+  const float* A = static_cast<const float*>(g.A);
+  const float* B = static_cast<const float*>(g.B);
+  float* C = static_cast<float*>(g.C);
+  if (!g.transA && !g.transB)
+    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, false, false><<<grid, block, 0, st>>>(A, B, C, p);
+  else if (!g.transA && g.transB)
+    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, false, true><<<grid, block, 0, st>>>(A, B, C, p);
+  else if (g.transA && !g.transB)
+    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, true, false><<<grid, block, 0, st>>>(A, B, C, p);
+  else
+    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, true, true><<<grid, block, 0, st>>>(A, B, C, p);
+  return (int)cudaGetLastError();
+}
+
+// The tcgen05 kernel addresses its operands through TMA: 16-byte aligned bases and
+// leading dimensions that are multiples of 8 fp16 elements.
+static bool hgemm_tma_ok(const GemmArgs& g) {
+  return aligned16(g.A) && aligned16(g.B) && aligned16(g.C) && g.lda % 8 == 0 && g.ldb % 8 == 0 &&
+         g.ldc % 8 == 0 && g.k > 0;
+}
+
+template <int TM, int STAGES, bool AK, bool BK_>
+static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                             const HgemmParams& p, unsigned grid, cudaStream_t st) {
+  using L = HgemmSmem<TM, STAGES>;
+  auto kern = hgemm_tcgen05_kernel<TM, STAGES, AK, BK_>;
+  static bool attr_done[kMaxDevices] = {};
+  const int dev = current_device();
+  if (dev >= 0 && dev < kMaxDevices && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess) return (int)e;
+    attr_done[dev] = true;
+  }
+  kern<<<grid, kHgemmThreads, L::kDynamic, st>>>(ta, tb, tc, p);
+  return (int)cudaGetLastError();
+}
+
+template <int TM, int STAGES>
+static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
+  CUtensorMap ta, tb, tc;
+  int rc;
+  // op(A): K-major when transposed (stored k x m), MN-major otherwise (stored m x k).
+  if (g.transA)
+    rc = make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.k, g.m, g.lda, kBlockK, TM);
+  else
+    rc = make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.m, g.k, g.lda, 64, kBlockK);
+  if (rc) return rc;
+  // op(B): K-major when not transposed (stored k x n), MN-major otherwise (stored n x k).
+  if (!g.transB)
+    rc = make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.B, g.k, g.n, g.ldb, kBlockK, kTileN);
+  else
+    rc = make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.B, g.n, g.k, g.ldb, 64, kBlockK);
+  if (rc) return rc;
+  rc = make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.C, g.m, g.n, g.ldc, 64, 32);
+  if (rc) return rc;
+
+  HgemmParams p;
+  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
+  p.tiles_m = (uint32_t)((g.m + TM - 1) / TM);
+  p.tiles_n = (uint32_t)((g.n + kTileN - 1) / kTileN);
+  p.wgm = wgm;
+  p.alpha = g.alpha; p.beta = g.beta;
+  const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
+  if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
+  const unsigned grid = (unsigned)(tiles < (uint64_t)sm_count() ? tiles : (uint64_t)sm_count());
+  if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, true, true>(ta, tb, tc, p, grid, st);
+  if (g.transA && g.transB) return launch_hgemm_inst<TM, STAGES, true, false>(ta, tb, tc, p, grid, st);
+  if (!g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, false, true>(ta, tb, tc, p, grid, st);
+  return launch_hgemm_inst<TM, STAGES, false, false>(ta, tb, tc, p, grid, st);
+}
+
+// ------------------------------------------------------------------ selection --------
+static int select_f32(const GemmArgs& g) {
+  if (g.k == 0) return 0;
+  const uint64_t big_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 127) / 128);
+  return big_tiles >= 2ull * (uint64_t)sm_count() ? 1 : 2;
+}
+
+static int select_f16(const GemmArgs& g) {
+  if (!hgemm_tma_ok(g)) return 0;
+  // Prefer the 256-wide tile unless the 128-wide one fills the SMs markedly better.
+  const double sms = (double)sm_count();
+  auto eff = [&](uint64_t tiles) {
+    const double waves = (double)((tiles + (uint64_t)sms - 1) / (uint64_t)sms);
+    return (double)tiles / (waves * sms);
+  };
+  const uint64_t t256 = (uint64_t)((g.m + 255) / 256) * ((g.n + 127) / 128);
+  const uint64_t t128 = (uint64_t)((g.m + 127) / 128) * ((g.n + 127) / 128);
+  if (g.m <= 128) return 2;
+  return eff(t256) >= 0.85 * eff(t128) ? 1 : 2;
+}
+
+static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
+  if (g.m == 0 || g.n == 0) return MMBO_OK;
+  if (g.k == 0) return launch_scale<float>(g, st);
+  switch (id) {
+    case 0: return launch_simple<float>(g, st);
+    case 1: return launch_sgemm_ffma<128, 128, 8, 8>(g, env_u32("MMBO_WGM", kF32Rows[1].wgm), st);
+    case 2: return launch_sgemm_ffma<64, 64, 4, 4>(g, env_u32("MMBO_WGM", kF32Rows[2].wgm), st);
+  }
+  return MMBO_ERR_BAD_KERNEL_ID;
+}
+
+static int run_f16(const GemmArgs& g, int id, cudaStream_t st) {
+  if (g.m == 0 || g.n == 0) return MMBO_OK;
+  if (g.k == 0) return launch_scale<__half>(g, st);
+  switch (id) {
+    case 0: return launch_simple<__half>(g, st);
+    case 1:
+      if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
+      return launch_hgemm_tcgen05<256, 4>(g, env_u32("MMBO_WGM", kF16Rows[1].wgm), st);
+    case 2:
+      if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
+      return launch_hgemm_tcgen05<128, 6>(g, env_u32("MMBO_WGM", kF16Rows[2].wgm), st);
+  }
+  return MMBO_ERR_BAD_KERNEL_ID;
+}
+
+}  // namespace mmbo
+
+// ====================================================================== C ABI =========
+using namespace mmbo;
+
+extern "C" {
+
+int mmbo_gemm_f32(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
+                  const float* A, size_t lda, const float* B, size_t ldb, const float* beta, float* C,
+                  size_t ldc, int kernelId, void* stream) {
+  GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
+  int rc = validate(g, alpha, beta);
+  if (rc) return rc;
+  g.alpha = *alpha;
+  g.beta = *beta;
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF32)) return MMBO_ERR_BAD_KERNEL_ID;
+  const int id = kernelId == MMBO_KERNEL_AUTO ? select_f32(g) : kernelId;
+  return run_f32(g, id, static_cast<cudaStream_t>(stream));
+}
+
+int mmbo_gemm_f16(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha, const void* A,
+                  size_t lda, const void* B, size_t ldb, const float* beta, void* C, size_t ldc,
+                  int kernelId, void* stream) {
+  GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
+  int rc = validate(g, alpha, beta);
+  if (rc) return rc;
+  g.alpha = *alpha;
+  g.beta = *beta;
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF16)) return MMBO_ERR_BAD_KERNEL_ID;
+  const int id = kernelId == MMBO_KERNEL_AUTO ? select_f16(g) : kernelId;
+  return run_f16(g, id, static_cast<cudaStream_t>(stream));
+}
+
+int mmbo_num_kernels(int dtype) {
+  int n = 0;
+  rows_of(dtype, &n);
+  return n;
+}
+
+const char* mmbo_kernel_name(int dtype, int kernelId) {
+  int n = 0;
+  const KernelRow* r = rows_of(dtype, &n);
+  if (!r || kernelId < 0 || kernelId >= n) return nullptr;
+  return r[kernelId].name;
+}
+
+int mmbo_kernel_params(int dtype, int kernelId, int out[8]) {
+  int n = 0;
+  const KernelRow* r = rows_of(dtype, &n);
+  if (!r) return MMBO_ERR_BAD_DTYPE;
+  if (kernelId < 0 || kernelId >= n) return MMBO_ERR_BAD_KERNEL_ID;
+  if (!out) return MMBO_ERR_NULL_POINTER;
+  const KernelRow& k = r[kernelId];
+  out[0] = k.mt0; out[1] = k.mt1; out[2] = k.threads; out[3] = k.depth_u;
+  out[4] = k.stages; out[5] = k.cta_group; out[6] = k.wgm; out[7] = k.tensor;
+  return MMBO_OK;
+}
+
+int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, size_t k, const void* A,
+                       size_t lda, const void* B, size_t ldb, const void* C, size_t ldc) {
+  GemmArgs g{transA, transB, m, n, k, A, B, const_cast<void*>(C), lda, ldb, ldc, 1.f, 0.f};
+  const float one = 1.f;
+  int rc = validate(g, &one, &one);
+  if (rc) return rc;
+  if (dtype == MMBO_DTYPE_F32) return select_f32(g);
+  if (dtype == MMBO_DTYPE_F16) return select_f16(g);
+  return MMBO_ERR_BAD_DTYPE;
+}
+
+const char* mmbo_status_string(int status) {
+  switch (status) {
+    case MMBO_OK: return "ok";
+    case MMBO_ERR_BAD_TRANS: return "transA/transB must be 0 or 1";
+    case MMBO_ERR_BAD_DIM: return "m, n or k out of range";
+    case MMBO_ERR_NULL_POINTER: return "null pointer argument";
+    case MMBO_ERR_BAD_LDA: return "lda smaller than the leading extent of A";
+    case MMBO_ERR_BAD_LDB: return "ldb smaller than the leading extent of B";
+    case MMBO_ERR_BAD_LDC: return "ldc smaller than m";
+    case MMBO_ERR_BAD_KERNEL_ID: return "kernelId outside the kernel table";
+    case MMBO_ERR_KERNEL_UNSUITABLE: return "forced kernel cannot address these operands (alignment)";
+    case MMBO_ERR_BAD_DTYPE: return "unknown dtype";
+    case MMBO_ERR_BAD_SHARD: return "bad shard arguments";
+    case MMBO_ERR_NO_DRIVER_ENTRY: return "cuTensorMapEncodeTiled unavailable";
+    case MMBO_ERR_TENSOR_MAP: return "tensor map rejected by the driver";
+    case MMBO_ERR_DEVICE_FAULT: return "a kernel recorded a bounded-wait time-out";
+    case MMBO_ERR_TOO_LARGE: return "problem exceeds launch limits of the chosen kernel";
+  }
+  if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  return "unknown status";
+}
+
+void mmbo_wgm_map(uint32_t wg0, uint32_t wg1, uint32_t nwg0, uint32_t nwg1, uint32_t wgm, uint32_t* tile0,
+                  uint32_t* tile1) {
+  mmbo_wgm_remap(wg0, wg1, nwg0, nwg1, wgm, tile0, tile1);
+}
+
+int mmbo_shard_columns(size_t n, int nGpus, int rank, size_t align, size_t* col0, size_t* ncols) {
+  if (nGpus <= 0 || rank < 0 || rank >= nGpus || !col0 || !ncols) return MMBO_ERR_BAD_SHARD;
+  if (align == 0) align = 1;
+  const size_t units = (n + align - 1) / align;  // column groups of `align`
+  const size_t base = units / (size_t)nGpus, extra = units % (size_t)nGpus;
+  const size_t r = (size_t)rank;
+  const size_t u0 = r * base + (r < extra ? r : extra);
+  const size_t un = base + (r < extra ? 1 : 0);
+  size_t c0 = u0 * align, c1 = (u0 + un) * align;
+  if (c0 > n) c0 = n;
+  if (c1 > n) c1 = n;
+  *col0 = c0;
+  *ncols = c1 - c0;
+  return MMBO_OK;
+}
+
+static int fill_common(int dtype, void* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat,
+                       int dist, float scale, size_t row0, size_t col0, size_t total_rows, void* stream) {
+  if (rows == 0 || cols == 0) return MMBO_OK;
+  if (!dst) return MMBO_ERR_NULL_POINTER;
+  if (ld < rows) return MMBO_ERR_BAD_LDC;
+  const size_t total = rows * cols;
+  size_t blocks = (total + 255) / 256;
+  const size_t cap = (size_t)sm_count() * 32;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == MMBO_DTYPE_F32)
+    fill_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(static_cast<float*>(dst), rows, cols, ld, seed, mat,
+                                                         dist, scale, row0, col0, total_rows);
+  else
+    fill_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<__half*>(dst), rows, cols, ld, seed,
+                                                          mat, dist, scale, row0, col0, total_rows);
+  return (int)cudaGetLastError();
+}
+
+int mmbo_fill_f32(float* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat, int dist,
+                  float scale, size_t row0, size_t col0, size_t total_rows, void* stream) {
+  return fill_common(MMBO_DTYPE_F32, dst, rows, cols, ld, seed, mat, dist, scale, row0, col0, total_rows, stream);
+}
+
+int mmbo_fill_f16(void* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat, int dist,
+                  float scale, size_t row0, size_t col0, size_t total_rows, void* stream) {
+  return fill_common(MMBO_DTYPE_F16, dst, rows, cols, ld, seed, mat, dist, scale, row0, col0, total_rows, stream);
+}
+
+int mmbo_device_status(unsigned int* status) {
+  if (!status) return MMBO_ERR_NULL_POINTER;
+  unsigned int v = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemcpyFromSymbol(&v, g_mmbo_device_status, sizeof v);
+  if (e != cudaSuccess) return (int)e;
+  if (v != 0) {
+    const unsigned int zero = 0;
+    e = cudaMemcpyToSymbol(g_mmbo_device_status, &zero, sizeof zero);
+    if (e != cudaSuccess) return (int)e;
+  }
+  *status = v;
+  return v ? MMBO_ERR_DEVICE_FAULT : MMBO_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,151 @@
+"""Python mirror of the reference's launch surface (src/gemm/gemm.h:4-5,47-48).
+
+`gemm()` takes the reference's argument list -- (m, n, k, alpha, A, lda, B, ldb, beta, C,
+ldc, kernelId) -- preceded by dtype and the two transpose flags; `sgemm_NT`, `hgemm_NT`,
+... are the per-layout wrappers named after the reference's `dgemm_NT`.  A, B and C are
+device buffers: torch CUDA tensors or raw device addresses.  Every call goes through
+the C ABI; errors come back as `MmboError` carrying the library's status code (the
+reference prints and exits: src/gemm/common.h:20-24).
+"""
+from __future__ import annotations
+
+import ctypes
+
+from ._lib import LIB
+
+DTYPE_F32, DTYPE_F16 = 0, 1
+KERNEL_AUTO = -1
+DIST_UNIFORM, DIST_NORMAL, DIST_ZERO = 0, 1, 2
+MAT_A, MAT_B, MAT_C = 0, 1, 2
+
+_DTYPES = {"f32": DTYPE_F32, "f16": DTYPE_F16, DTYPE_F32: DTYPE_F32, DTYPE_F16: DTYPE_F16}
+
+
+class MmboError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: status {status}: {status_string(status)}")
+
+
+def status_string(status: int) -> str:
+    s = LIB.mmbo_status_string(int(status))
+    return s.decode() if s else "?"
+
+
+def _addr(x) -> int | None:
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    return int(x.data_ptr())  # torch tensor
+
+
+def _stream(stream) -> int | None:
+    if stream is None:
+        try:
+            import torch
+            if torch.cuda.is_available():
+                return int(torch.cuda.current_stream().cuda_stream) or None
+        except ImportError:
+            pass
+        return None
+    if isinstance(stream, int):
+        return stream or None
+    return int(stream.cuda_stream) or None
+
+
+def gemm(dtype, transA: bool, transB: bool, m: int, n: int, k: int, alpha: float, A, lda: int, B,
+         ldb: int, beta: float, C, ldc: int, kernelId: int = KERNEL_AUTO, stream=None) -> None:
+    """C = alpha*op(A)*op(B) + beta*C on the current device, asynchronously on `stream`
+    (default: torch's current stream)."""
+    dt = _DTYPES[dtype]
+    fn = LIB.mmbo_gemm_f32 if dt == DTYPE_F32 else LIB.mmbo_gemm_f16
+    a, b = ctypes.c_float(alpha), ctypes.c_float(beta)
+    rc = fn(int(bool(transA)), int(bool(transB)), m, n, k, ctypes.byref(a), _addr(A), lda, _addr(B), ldb,
+            ctypes.byref(b), _addr(C), ldc, kernelId, _stream(stream))
+    if rc != 0:
+        raise MmboError(rc, "mmbo_gemm_f32" if dt == DTYPE_F32 else "mmbo_gemm_f16")
+
+
+def _wrap(dtype, ta, tb):
+    def f(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId=KERNEL_AUTO, stream=None):
+        gemm(dtype, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId, stream)
+    f.__doc__ = (f"{'s' if dtype == 'f32' else 'h'}gemm_{'T' if ta else 'N'}{'T' if tb else 'N'}: "
+                 "argument order of the reference's dgemm_NT (src/gemm/gemm.h:47-48).")
+    return f
+
+
+sgemm_NN, sgemm_NT = _wrap("f32", False, False), _wrap("f32", False, True)
+sgemm_TN, sgemm_TT = _wrap("f32", True, False), _wrap("f32", True, True)
+hgemm_NN, hgemm_NT = _wrap("f16", False, False), _wrap("f16", False, True)
+hgemm_TN, hgemm_TT = _wrap("f16", True, False), _wrap("f16", True, True)
+
+
+def num_kernels(dtype) -> int:
+    return int(LIB.mmbo_num_kernels(_DTYPES[dtype]))
+
+
+def kernel_name(dtype, kernel_id: int) -> str:
+    s = LIB.mmbo_kernel_name(_DTYPES[dtype], kernel_id)
+    if s is None:
+        raise MmboError(-7, "mmbo_kernel_name")
+    return s.decode()
+
+
+def kernel_params(dtype, kernel_id: int) -> dict:
+    out = (ctypes.c_int * 8)()
+    rc = LIB.mmbo_kernel_params(_DTYPES[dtype], kernel_id, out)
+    if rc != 0:
+        raise MmboError(rc, "mmbo_kernel_params")
+    keys = ("MT0", "MT1", "threads", "DepthU", "stages", "ctaGroup", "wgm", "tensorCores")
+    return dict(zip(keys, list(out)))
+
+
+def kernel_table(dtype) -> list[dict]:
+    """The counterpart of the tables in src/gemm/constants.h:4-135."""
+    return [{"id": i, "name": kernel_name(dtype, i), **kernel_params(dtype, i)}
+            for i in range(num_kernels(dtype))]
+
+
+def select_kernel(dtype, transA, transB, m, n, k, A, lda, B, ldb, C, ldc) -> int:
+    rc = LIB.mmbo_select_kernel(_DTYPES[dtype], int(bool(transA)), int(bool(transB)), m, n, k, _addr(A), lda,
+                                _addr(B), ldb, _addr(C), ldc)
+    if rc < 0:
+        raise MmboError(rc, "mmbo_select_kernel")
+    return rc
+
+
+def wgm_map(wg0: int, wg1: int, nwg0: int, nwg1: int, wgm: int) -> tuple[int, int]:
+    a, b = ctypes.c_uint32(), ctypes.c_uint32()
+    LIB.mmbo_wgm_map(wg0, wg1, nwg0, nwg1, wgm, ctypes.byref(a), ctypes.byref(b))
+    return a.value, b.value
+
+
+def shard_columns(n: int, n_gpus: int, rank: int, align: int = 128) -> tuple[int, int]:
+    """(first column, number of columns) of B/C owned by `rank`."""
+    c0, nc = ctypes.c_size_t(), ctypes.c_size_t()
+    rc = LIB.mmbo_shard_columns(n, n_gpus, rank, align, ctypes.byref(c0), ctypes.byref(nc))
+    if rc != 0:
+        raise MmboError(rc, "mmbo_shard_columns")
+    return c0.value, nc.value
+
+
+def fill(dtype, dst, rows: int, cols: int, ld: int, *, seed: int = 1234, mat: int = 0, dist: int = 0,
+         scale: float = 1.0, row0: int = 0, col0: int = 0, total_rows: int | None = None,
+         stream=None) -> None:
+    """Seeded operand generation on the device (include/mmbo_rng.h)."""
+    dt = _DTYPES[dtype]
+    fn = LIB.mmbo_fill_f32 if dt == DTYPE_F32 else LIB.mmbo_fill_f16
+    rc = fn(_addr(dst), rows, cols, ld, seed, mat, dist, float(scale), row0, col0,
+            rows if total_rows is None else total_rows, _stream(stream))
+    if rc != 0:
+        raise MmboError(rc, "mmbo_fill")
+
+
+def device_status() -> int:
+    """Synchronise the device; return its fault word (0 = none) and clear it."""
+    v = ctypes.c_uint32()
+    rc = LIB.mmbo_device_status(ctypes.byref(v))
+    if rc > 0:
+        raise MmboError(rc, "mmbo_device_status")
+    return v.value

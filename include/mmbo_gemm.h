@@ -1,0 +1,110 @@
+/*
+ * mmbo_gemm.h -- C ABI of libmmbo_gemm.so, the B200 (sm_100a) GEMM library that stands
+ * in for the launch surface of CSWater/GEMM_MMBO (src/gemm/gemm.h, src/gemm/driver.h,
+ * src/gemm/constants.h).  Plain pointers and sizes only.
+ *
+ * Conventions (all entry points):
+ *   - matrices are column-major; op(A) is m x k, op(B) is k x n, C is m x n;
+ *       transA == 0: A is stored m x k, lda >= m      transA != 0: stored k x m, lda >= k
+ *       transB == 0: B is stored k x n, ldb >= k      transB != 0: stored n x k, ldb >= n
+ *     so transA = 0, transB = 1 is the reference's only layout ("NT", ldb >= n:
+ *     src/gemm/benchmark.cc:26,111);
+ *   - A, B, C are DEVICE pointers owned by the caller; alpha and beta are HOST pointers
+ *     read during the call (src/gemm/gemm.h:31-32,76-77);
+ *   - C = beta != 0 ? alpha*op(A)*op(B) + beta*C : alpha*op(A)*op(B); with beta == 0 the
+ *     old contents of C are never read (src/gemm/ref/Kernels.cpp:87);
+ *   - the work is queued on `stream` (a cudaStream_t; NULL = the default stream, which
+ *     is what the reference uses: src/gemm/driver.h:56-59) and the call returns without
+ *     waiting for it;
+ *   - the return value is 0 on success, negative for a rejected argument (see
+ *     mmbo_status_string), positive for a CUDA runtime error code.  Nothing is printed
+ *     and the process is never terminated (the reference prints and calls exit(0):
+ *     src/gemm/common.h:20-24).
+ */
+#ifndef MMBO_GEMM_H_
+#define MMBO_GEMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MMBO_DTYPE_F32 0
+#define MMBO_DTYPE_F16 1
+
+#define MMBO_KERNEL_AUTO (-1)
+
+/* status codes */
+#define MMBO_OK 0
+#define MMBO_ERR_BAD_TRANS (-1)
+#define MMBO_ERR_BAD_DIM (-2)
+#define MMBO_ERR_NULL_POINTER (-3)
+#define MMBO_ERR_BAD_LDA (-4)
+#define MMBO_ERR_BAD_LDB (-5)
+#define MMBO_ERR_BAD_LDC (-6)
+#define MMBO_ERR_BAD_KERNEL_ID (-7)
+#define MMBO_ERR_KERNEL_UNSUITABLE (-8) /* forced kernel id cannot run these operands */
+#define MMBO_ERR_BAD_DTYPE (-9)
+#define MMBO_ERR_BAD_SHARD (-10)
+#define MMBO_ERR_NO_DRIVER_ENTRY (-11)  /* cuTensorMapEncodeTiled not available */
+#define MMBO_ERR_TENSOR_MAP (-12)       /* the driver rejected a tensor map */
+#define MMBO_ERR_DEVICE_FAULT (-13)     /* a kernel recorded a bounded-wait time-out */
+#define MMBO_ERR_TOO_LARGE (-14)
+
+/* SGEMM, fp32 storage and arithmetic.  Replaces dgemm_NT / naive_dgemm
+ * (src/gemm/gemm.h:47-48, :4-5) for dtype fp32; kernelId indexes the fp32 kernel table
+ * (mmbo_kernel_name) the way the reference's kernelId indexes constants.h:49-135, and
+ * MMBO_KERNEL_AUTO lets the library choose. */
+int mmbo_gemm_f32(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
+                  const float* A, size_t lda, const float* B, size_t ldb, const float* beta,
+                  float* C, size_t ldc, int kernelId, void* stream);
+
+/* HGEMM: IEEE binary16 storage for A, B, C (passed as void*), fp32 accumulation and fp32
+ * alpha/beta.  Same role as above for dtype fp16 (src/gemm/gemm.h:47-48). */
+int mmbo_gemm_f16(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
+                  const void* A, size_t lda, const void* B, size_t ldb, const float* beta,
+                  void* C, size_t ldc, int kernelId, void* stream);
+
+/* Kernel table -- the counterpart of naive_kernels / kernels / *_kernel_parameters in
+ * src/gemm/constants.h:4-135.  out[8] = {MT0 (tile along m), MT1 (tile along n), threads,
+ * DepthU (k per stage), stages, ctaGroup, wgm, usesTensorCores}. */
+int mmbo_num_kernels(int dtype);
+const char* mmbo_kernel_name(int dtype, int kernelId);
+int mmbo_kernel_params(int dtype, int kernelId, int out[8]);
+/* Kernel id that MMBO_KERNEL_AUTO resolves to for these operands (same checks as the
+ * gemm call; A, B, C may be any pointers with the alignment of the real ones). */
+int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, size_t k,
+                       const void* A, size_t lda, const void* B, size_t ldb, const void* C,
+                       size_t ldc);
+
+const char* mmbo_status_string(int status);
+
+/* Tile rasterisation used by the kernels (the reference's work-group mapping,
+ * src/gemm/ref/Kernels.cpp:209-236), exposed for host-side checks. */
+void mmbo_wgm_map(uint32_t wg0, uint32_t wg1, uint32_t nwg0, uint32_t nwg1, uint32_t wgm,
+                  uint32_t* tile0, uint32_t* tile1);
+
+/* Column-block partition of an n-column B/C among nGpus ranks: rank r owns columns
+ * [*col0, *col0 + *ncols).  Blocks are multiples of `align` columns except the last. */
+int mmbo_shard_columns(size_t n, int nGpus, int rank, size_t align, size_t* col0, size_t* ncols);
+
+/* Seeded operand generator on the device (replaces the rand()/RAND_MAX host loops of
+ * src/gemm/benchmark.cc:44-52): fills the rows x cols window of a column-major array with
+ * the values of logical elements (row0 + i, col0 + j) of matrix `mat` (mmbo_rng.h). */
+int mmbo_fill_f32(float* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat,
+                  int dist, float scale, size_t row0, size_t col0, size_t total_rows, void* stream);
+int mmbo_fill_f16(void* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat,
+                  int dist, float scale, size_t row0, size_t col0, size_t total_rows, void* stream);
+
+/* Reads and clears the device status word of the current device (synchronises the
+ * device).  *status = 0 when no kernel has recorded a fault since the last call;
+ * otherwise (code << 24) | detail of the first one.  Returns MMBO_OK, a CUDA error, or
+ * MMBO_ERR_DEVICE_FAULT when *status != 0. */
+int mmbo_device_status(unsigned int* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MMBO_GEMM_H_ */

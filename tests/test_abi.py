@@ -1,0 +1,105 @@
+"""Host-only checks of the C ABI: the library loads, exports every symbol the header
+declares, describes its kernel table, partitions columns and rejects bad arguments
+before anything is launched."""
+import ctypes
+import pathlib
+import re
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+def test_exports_every_declared_symbol(mm):
+    from gemm_mmbo_b200 import _lib
+    header = (ROOT / "include" / "mmbo_gemm.h").read_text()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(mmbo_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations parsed"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    raw = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in declared:
+        assert hasattr(raw, name), name
+
+
+def test_kernel_tables(mm):
+    for dt in ("f32", "f16"):
+        table = mm.kernel_table(dt)
+        assert len(table) >= 3
+        names = [r["name"] for r in table]
+        assert len(set(names)) == len(names)
+        for r in table:
+            assert r["MT0"] > 0 and r["MT1"] > 0 and r["threads"] % 32 == 0
+            # name carries the macro-tile like the reference's kernel names
+            assert f"MT{r['MT0']:03d}x{r['MT1']:03d}x{r['DepthU']:02d}" in r["name"]
+    assert any(r["tensorCores"] for r in mm.kernel_table("f16"))
+    with pytest.raises(mm.MmboError):
+        mm.kernel_name("f16", 99)
+    with pytest.raises(mm.MmboError):
+        mm.kernel_params("f32", -1)
+
+
+@pytest.mark.parametrize("n,p,align", [(32768, 8, 128), (32768, 1, 128), (1000, 3, 128), (130, 4, 128),
+                                       (5, 8, 1), (0, 2, 128), (4097, 8, 64)])
+def test_shard_columns_partition(mm, n, p, align):
+    blocks = [mm.shard_columns(n, p, r, align) for r in range(p)]
+    pos = 0
+    for c0, nc in blocks:
+        assert c0 == pos
+        pos += nc
+    assert pos == n
+    sizes = [nc for _, nc in blocks]
+    assert max(sizes) - min(sizes) < 2 * align
+    for c0, nc in blocks[:-1]:
+        assert nc % align == 0 or c0 + nc == n
+
+
+def test_shard_columns_rejects(mm):
+    for args in [(10, 0, 0, 1), (10, 2, 2, 1), (10, 2, -1, 1)]:
+        with pytest.raises(mm.MmboError):
+            mm.shard_columns(*args)
+
+
+def test_status_strings(mm):
+    assert mm.status_string(0) == "ok"
+    for code in range(-14, 0):
+        assert mm.status_string(code) not in ("", "unknown status")
+
+
+BAD = 0x1000  # a non-null, 16-byte aligned address that is never dereferenced on these paths
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+def test_rejects_bad_arguments_before_launch(mm, dtype):
+    ok = dict(transA=False, transB=True, m=64, n=32, k=16, alpha=1.0, A=BAD, lda=64, B=BAD, ldb=32,
+              beta=0.0, C=BAD, ldc=64, kernelId=-1)
+
+    def status(**kw):
+        a = {**ok, **kw}
+        try:
+            mm.gemm(dtype, a["transA"], a["transB"], a["m"], a["n"], a["k"], a["alpha"], a["A"], a["lda"],
+                    a["B"], a["ldb"], a["beta"], a["C"], a["ldc"], a["kernelId"], stream=0)
+        except mm.MmboError as e:
+            return e.status
+        return 0
+
+    assert status(lda=63) == -4          # NT: lda >= m
+    assert status(ldb=31) == -5          # NT: ldb >= n
+    assert status(ldc=63) == -6
+    assert status(transA=True, lda=15) == -4   # TN: lda >= k
+    assert status(transB=False, ldb=15) == -5  # NN: ldb >= k
+    assert status(A=None) == -3 and status(B=None) == -3 and status(C=None) == -3
+    assert status(kernelId=99) == -7 and status(kernelId=-2) == -7
+    assert status(m=2 ** 31) == -2
+    # empty problems are accepted and launch nothing
+    assert status(m=0) == 0 and status(n=0) == 0
+
+
+def test_raw_abi_rejects_bad_trans_and_null_scalars(mm):
+    from gemm_mmbo_b200._lib import LIB
+    one = ctypes.c_float(1.0)
+    args = [64, 32, 16, ctypes.byref(one), BAD, 64, BAD, 32, ctypes.byref(one), BAD, 64, -1, None]
+    assert LIB.mmbo_gemm_f32(2, 0, *args) == -1
+    assert LIB.mmbo_gemm_f16(0, -1, *args) == -1
+    args[3] = None
+    assert LIB.mmbo_gemm_f32(0, 1, *args) == -3

@@ -1,0 +1,74 @@
+"""HGEMM parity (fp16 storage, fp32 accumulation): every fp16 kernel of the table and
+automatic selection against the oracle, relative Frobenius error <= 2e-3."""
+import numpy as np
+import pytest
+
+from helpers import Case, run_and_check
+
+pytestmark = pytest.mark.gpu
+
+MODES = [(False, False), (False, True), (True, False), (True, True)]
+# 0/1/several/partial tiles of the 256x128 and 128x128 macro-tiles; K tails of the
+# 64-deep stage; more tiles than stages and than accumulators
+SHAPES = [(8, 8, 8), (64, 32, 16), (128, 128, 64), (256, 128, 128), (136, 72, 200), (264, 136, 72),
+          (520, 392, 328), (1024, 512, 640), (40, 1000, 96), (1000, 40, 96)]
+
+
+@pytest.mark.parametrize("kernel_id", [1, 2, -1, 0])
+@pytest.mark.parametrize("ta,tb", MODES)
+def test_hgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
+    for (m, n, k) in SHAPES:
+        for pad, beta in (((0, 0, 0), 0.5), ((8, 16, 24), -0.25), ((0, 8, 0), 0.0)):
+            case = Case(oracle, "f16", ta, tb, m, n, k, 1.0 if beta else 0.75, beta, pad=pad,
+                        seed=m * 7 + n, dist=oracle.DIST_NORMAL, scale=0.5)
+            run_and_check(cuda, mm, case, kernel_id)
+
+
+@pytest.mark.parametrize("kernel_id", [1, 2, -1, 0])
+def test_hgemm_beta_zero_never_reads_c(cuda, mm, oracle, kernel_id):
+    case = Case(oracle, "f16", False, True, 264, 200, 72, 2.0, 0.0, pad=(0, 8, 16), c_poison=True)
+    run_and_check(cuda, mm, case, kernel_id)
+
+
+@pytest.mark.parametrize("kernel_id", [1, 2, -1])
+def test_hgemm_many_tiles_per_cta(cuda, mm, oracle, kernel_id):
+    """More tiles than SMs: every persistent CTA walks several tiles, so stage and
+    accumulator phases wrap many times."""
+    case = Case(oracle, "f16", False, True, 4096 + 8, 2048 + 8, 136, 1.0, 0.5, dist=oracle.DIST_NORMAL,
+                scale=0.5)
+    run_and_check(cuda, mm, case, kernel_id)
+
+
+def test_hgemm_unaligned_operands_take_the_general_path(cuda, mm, oracle):
+    """Leading dimensions that are not multiples of 8 cannot be described to TMA; the
+    automatic choice must fall back and a forced tensor-core kernel must refuse."""
+    case = Case(oracle, "f16", False, True, 100, 60, 50, 1.0, 0.5, pad=(3, 3, 3))
+    run_and_check(cuda, mm, case, -1)
+    from helpers import to_device
+    _, dA = to_device(cuda, case.A)
+    _, dB = to_device(cuda, case.B)
+    _, dC = to_device(cuda, case.C)
+    assert mm.select_kernel("f16", False, True, 100, 60, 50, dA, case.lda, dB, case.ldb, dC, case.ldc) == 0
+    with pytest.raises(mm.MmboError) as e:
+        mm.gemm("f16", False, True, 100, 60, 50, 1.0, dA, case.lda, dB, case.ldb, 0.5, dC, case.ldc, 1)
+    assert e.value.status == -8
+
+
+def test_hgemm_k_zero_and_empty(cuda, mm, oracle):
+    run_and_check(cuda, mm, Case(oracle, "f16", False, False, 72, 40, 0, 2.0, 0.5, pad=(0, 0, 8)), -1)
+    run_and_check(cuda, mm, Case(oracle, "f16", False, False, 0, 40, 16, 1.0, 0.5), -1)
+
+
+def test_hgemm_tensor_kernels_agree_bitwise_across_runs(cuda, mm, oracle):
+    from helpers import to_device
+    torch = cuda
+    case = Case(oracle, "f16", True, False, 520, 392, 328, 1.0, 0.5)
+    outs = []
+    for _ in range(2):
+        _, dA = to_device(torch, case.A)
+        _, dB = to_device(torch, case.B)
+        _, dC = to_device(torch, case.C)
+        mm.gemm("f16", True, False, 520, 392, 328, 1.0, dA, case.lda, dB, case.ldb, 0.5, dC, case.ldc, 1)
+        torch.cuda.synchronize()
+        outs.append(dC.cpu().numpy().view(np.uint16))
+    assert np.array_equal(outs[0], outs[1])

@@ -1,0 +1,60 @@
+"""SGEMM parity: every fp32 kernel of the table (and automatic selection) against the
+oracle, relative Frobenius error <= 1e-5, all transpose modes, ragged shapes, padded
+leading dimensions, guard bands, beta == 0 with poisoned C."""
+import pytest
+
+from helpers import Case, run_and_check
+
+pytestmark = pytest.mark.gpu
+
+MODES = [(False, False), (False, True), (True, False), (True, True)]
+# shapes chosen to give 0, 1, several and partial tiles in each dimension of the
+# 128x128 and 64x64 macro-tiles, and K tails of the 16-deep slab
+SHAPES = [(1, 1, 1), (5, 3, 2), (64, 64, 16), (65, 63, 17), (128, 128, 32), (129, 127, 33),
+          (200, 300, 100), (384, 256, 64), (257, 513, 129)]
+
+
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, -1])
+@pytest.mark.parametrize("ta,tb", MODES)
+def test_sgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
+    for (m, n, k) in SHAPES:
+        for pad in ((0, 0, 0), (3, 3, 3), (4, 8, 12)):
+            case = Case(oracle, "f32", ta, tb, m, n, k, 1.5, -0.25, pad=pad, seed=m * 1000 + n)
+            run_and_check(cuda, mm, case, kernel_id)
+
+
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, -1])
+def test_sgemm_beta_zero_never_reads_c(cuda, mm, oracle, kernel_id):
+    case = Case(oracle, "f32", False, True, 150, 70, 40, 2.0, 0.0, pad=(1, 2, 3), c_poison=True)
+    run_and_check(cuda, mm, case, kernel_id)
+
+
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, -1])
+def test_sgemm_k_zero_scales_c(cuda, mm, oracle, kernel_id):
+    case = Case(oracle, "f32", False, False, 70, 33, 0, 2.0, 0.5, pad=(0, 0, 5))
+    run_and_check(cuda, mm, case, kernel_id)
+    case = Case(oracle, "f32", False, False, 70, 33, 0, 2.0, 0.0, pad=(0, 0, 5), c_poison=True)
+    run_and_check(cuda, mm, case, kernel_id)
+
+
+def test_sgemm_empty(cuda, mm, oracle):
+    for (m, n) in ((0, 5), (5, 0), (0, 0)):
+        case = Case(oracle, "f32", False, False, m, n, 7, 1.0, 1.0)
+        run_and_check(cuda, mm, case, -1)
+
+
+def test_sgemm_deterministic(cuda, mm, oracle):
+    """Two runs of the same kernel give bit-identical C."""
+    import numpy as np
+    from helpers import to_device
+    torch = cuda
+    case = Case(oracle, "f32", True, False, 300, 260, 190, 1.0, 0.0)
+    outs = []
+    for _ in range(2):
+        _, dA = to_device(torch, case.A)
+        _, dB = to_device(torch, case.B)
+        _, dC = to_device(torch, case.C)
+        mm.gemm("f32", True, False, 300, 260, 190, 1.0, dA, case.lda, dB, case.ldb, 0.0, dC, case.ldc, 1)
+        torch.cuda.synchronize()
+        outs.append(dC.cpu().numpy().view(np.uint32))
+    assert np.array_equal(outs[0], outs[1])
