@@ -46,10 +46,14 @@ constexpr int kEpiWarps = 4;
 constexpr int kEpiBufBytes = 32 * 128;  // 32 C columns x 64 rows of fp16, per warp buffer
 constexpr int kHgemmThreads = 192;
 
-template <int TM, int STAGES>
+// CG = CTAs cooperating on one UMMA (cta_group): 1, or 2 for a CTA pair that shares a
+// 256-lane accumulator; each CTA of a pair stages its own 128 rows of op(B) and its own
+// half (TM / 2 rows) of op(A).
+template <int TM, int STAGES, int CG = 1>
 struct HgemmSmem {
+  static constexpr int kAopRows = TM / CG;                // rows of op(A) staged by one CTA
   static constexpr int kBopBytes = kTileN * kBlockK * 2;  // op(B) tile  (UMMA A operand)
-  static constexpr int kAopBytes = TM * kBlockK * 2;      // op(A) tile  (UMMA B operand)
+  static constexpr int kAopBytes = kAopRows * kBlockK * 2;  // op(A) tile  (UMMA B operand)
   static constexpr int kStageBytes = kBopBytes + kAopBytes;
   static constexpr int kEpiOffset = STAGES * kStageBytes;
   static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiBufBytes;
@@ -63,19 +67,35 @@ struct HgemmSmem {
 
 struct HgemmParams {
   uint32_t m, n, k;
-  uint32_t tiles_m, tiles_n;  // ceil(m / TM), ceil(n / 128)
+  uint32_t tiles_m, tiles_n;  // ceil(m / TM), ceil(n / (128 * CG))
   uint32_t wgm;               // work-group-mapping width (tile columns per block)
   float alpha, beta;
 };
 
-template <int TM, int STAGES, bool A_KMAJOR, bool B_KMAJOR>
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int TM, int STAGES, bool A_KMAJOR, bool B_KMAJOR, int CG = 1>
 __global__ void __launch_bounds__(kHgemmThreads, 1)
 hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_c, const HgemmParams p) {
-  using L = HgemmSmem<TM, STAGES>;
+  using L = HgemmSmem<TM, STAGES, CG>;
   static_assert(TM == 128 || TM == 256, "TM is the UMMA N extent");
+  static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair per UMMA");
   constexpr uint32_t kTmemCols = 2 * TM;
+  // CTA pair: rank 0 (the leader) issues every UMMA and owns the barriers that count
+  // both CTAs' copies; this CTA's index among the tile walkers is its cluster's index.
+  const uint32_t cta_rank = (CG == 2) ? cluster_cta_rank() : 0u;
+  const uint32_t walker = blockIdx.x / CG;
+  const uint32_t num_walkers = gridDim.x / CG;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -104,7 +124,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (uint32_t a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), kEpiWarps);
+      mbar_init(tmem_empty_bar(a), kEpiWarps * CG);
     }
     for (uint32_t w = 0; w < kEpiWarps; ++w)
       for (uint32_t b = 0; b < 2; ++b) mbar_init(cload_bar(w, b), 1);
@@ -115,11 +135,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   __syncwarp();
   if (warp == 1) {
-    tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
-    tmem_relinquish<1>();
+    tmem_alloc<CG>(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
+    tmem_relinquish<CG>();
   }
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // peer's barriers and tensor memory are ready
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
 
@@ -129,34 +150,41 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, issued = 0;
       bool ok = true;
-      for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers) {
         uint32_t tm_idx, tn_idx;
         mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
-        const int32_t m0 = static_cast<int32_t>(tm_idx * TM);
-        const int32_t n0 = static_cast<int32_t>(tn_idx * kTileN);
+        // This CTA's share of the tile: its own 128 columns of C (rows of op(B)^T) and
+        // its own TM / CG rows of op(A).
+        const int32_t m0 = static_cast<int32_t>(tm_idx * TM + cta_rank * L::kAopRows);
+        const int32_t n0 = static_cast<int32_t>((tn_idx * CG + cta_rank) * kTileN);
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kFaultWaitEmpty, stage)) {
             ok = false;
             break;
           }
-          const uint32_t bar = full_bar(stage);
+          // Completion is counted on the leader's barrier, which expects both CTAs' bytes.
+          const uint32_t bar = (CG == 2) ? mapa_shared(full_bar(stage), 0u) : full_bar(stage);
           const uint32_t s_bop = smem_base + stage * L::kStageBytes;
           const uint32_t s_aop = s_bop + L::kBopBytes;
           const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
-          mbar_expect_tx(bar, L::kStageBytes);
+          if (cta_rank == 0) mbar_expect_tx(full_bar(stage), L::kStageBytes * CG);
+          auto load = [&](uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1) {
+            if constexpr (CG == 2) tma_load_2d_pair(dst, map, bar, c0, c1);
+            else tma_load_2d(dst, map, bar, c0, c1);
+          };
           if constexpr (B_KMAJOR) {
-            tma_load_2d(s_bop, &tmap_b, bar, k0, n0);  // box {64 k, 128 n}
+            load(s_bop, &tmap_b, k0, n0);  // box {64 k, 128 n}
           } else {
 #pragma unroll
             for (int c = 0; c < kTileN / 64; ++c)  // boxes {64 n, 64 k}
-              tma_load_2d(s_bop + c * 8192, &tmap_b, bar, n0 + 64 * c, k0);
+              load(s_bop + c * 8192, &tmap_b, n0 + 64 * c, k0);
           }
           if constexpr (A_KMAJOR) {
-            tma_load_2d(s_aop, &tmap_a, bar, k0, m0);  // box {64 k, TM m}
+            load(s_aop, &tmap_a, k0, m0);  // box {64 k, TM / CG m}
           } else {
 #pragma unroll
-            for (int c = 0; c < TM / 64; ++c)  // boxes {64 m, 64 k}
-              tma_load_2d(s_aop + c * 8192, &tmap_a, bar, m0 + 64 * c, k0);
+            for (int c = 0; c < L::kAopRows / 64; ++c)  // boxes {64 m, 64 k}
+              load(s_aop + c * 8192, &tmap_a, m0 + 64 * c, k0);
           }
           ++issued;
           if (++stage == STAGES) {
@@ -165,9 +193,11 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
-      if (!ok) {
+      if (!ok && cta_rank == 0) {
         // Unwind: let every copy this thread issued land before the CTA's shared
         // memory is released.  A stage already consumed reports complete at once.
+        // (In a CTA pair the leader's barriers count both CTAs' copies, and neither CTA
+        // leaves before the cluster barrier at the end of the kernel.)
         uint32_t s = stage, ph = phase;
         const uint32_t back = issued < STAGES ? issued : STAGES;
         for (uint32_t i = 0; i < back; ++i) {
@@ -183,16 +213,16 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ===== UMMA issuer =====
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(0u, B_KMAJOR ? 0u : 1u, A_KMAJOR ? 0u : 1u, kTileN, TM);
+    // ===== UMMA issuer (leader CTA of a pair) =====
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc(0u, B_KMAJOR ? 0u : 1u, A_KMAJOR ? 0u : 1u, kTileN * CG, TM);
       constexpr uint32_t kStepBop = B_KMAJOR ? 32u : 2048u;  // bytes per UMMA K step
       constexpr uint32_t kStepAop = A_KMAJOR ? 32u : 2048u;
       constexpr uint32_t kLboBop = B_KMAJOR ? 16u : 8192u;
       constexpr uint32_t kLboAop = A_KMAJOR ? 16u : 8192u;
       uint32_t stage = 0, phase = 0, local_tile = 0;
       bool ok = true;
-      for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+      for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers, ++local_tile) {
         const uint32_t acc = local_tile & 1u;
         const uint32_t acc_phase = (local_tile >> 1) & 1u;
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, kFaultWaitTmemEmpty, acc)) {
@@ -213,16 +243,21 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t desc_b = make_smem_desc_sw128(s_aop, kLboAop, 1024u);
 #pragma unroll
           for (uint32_t j = 0; j < kBlockK / kUmmaK; ++j) {
-            umma_ss<1, false>(d_tmem, desc_a + ((j * kStepBop) >> 4), desc_b + ((j * kStepAop) >> 4),
-                              idesc, (kb | j) != 0u ? 1u : 0u);
+            umma_ss<CG, false>(d_tmem, desc_a + ((j * kStepBop) >> 4), desc_b + ((j * kStepAop) >> 4),
+                               idesc, (kb | j) != 0u ? 1u : 0u);
           }
-          umma_commit(empty_bar(stage));  // frees the stage once these UMMAs have read it
+          // frees the stage (in both CTAs of a pair) once these UMMAs have read it
+          if constexpr (CG == 2) umma_commit_pair(empty_bar(stage), 3);
+          else umma_commit(empty_bar(stage));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(tmem_full_bar(acc));  // accumulator complete
+        if (ok) {  // accumulator complete (in both CTAs of a pair)
+          if constexpr (CG == 2) umma_commit_pair(tmem_full_bar(acc), 3);
+          else umma_commit(tmem_full_bar(acc));
+        }
       }
     }
     __syncwarp();
@@ -237,11 +272,11 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t local_tile = 0, chunk_ctr = 0;
     uint32_t cphase[2] = {0u, 0u};
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+    for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers, ++local_tile) {
       uint32_t tm_idx, tn_idx;
       mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
       const uint32_t m0 = tm_idx * TM;
-      const uint32_t ncol0 = tn_idx * kTileN + 32u * q;  // first C column of this warp
+      const uint32_t ncol0 = (tn_idx * CG + cta_rank) * kTileN + 32u * q;  // first C column of this warp
       const uint32_t acc = local_tile & 1u;
       const uint32_t acc_phase = (local_tile >> 1) & 1u;
       // Every lane polls; the verdict is made warp-uniform so that the aligned
@@ -283,7 +318,10 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // Accumulator fully read: hand it back to the UMMA issuer.
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+            if (lane == 0) {
+              if constexpr (CG == 2) mbar_arrive_cluster(mapa_shared(tmem_empty_bar(acc), 0u));
+              else mbar_arrive(tmem_empty_bar(acc));
+            }
           }
 #pragma unroll
           for (uint32_t jj = 0; jj < 4; ++jj) {
@@ -325,9 +363,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // ------------------------------------------------------------------ teardown ------
   tcgen05_fence_before();
   __syncthreads();
+  // A CTA of a pair must outlive every access its peer makes to its shared memory,
+  // barriers and tensor memory.
+  if constexpr (CG == 2) cluster_sync_all();
   if (warp == 1) {
     tcgen05_fence_after();
-    tmem_dealloc<1>(tmem_base, kTmemCols);
+    tmem_dealloc<CG>(tmem_base, kTmemCols);
   }
 }
 

@@ -35,6 +35,7 @@ static const KernelRow kF16Rows[] = {
     {"hgemm_simple_MT032x008x01_TT01_01_WG256", 32, 8, 256, 1, 1, 1, 1, 0},
     {"hgemm_tcgen05_MT256x128x64_S4_CG1_WG192_WGM08", 256, 128, 192, 64, 4, 1, 8, 1},
     {"hgemm_tcgen05_MT128x128x64_S6_CG1_WG192_WGM08", 128, 128, 192, 64, 6, 1, 8, 1},
+    {"hgemm_tcgen05_MT256x256x64_S6_CG2_WG192_WGM08", 256, 256, 192, 64, 6, 2, 8, 1},
 };
 constexpr int kNumF32 = sizeof(kF32Rows) / sizeof(KernelRow);
 constexpr int kNumF16 = sizeof(kF16Rows) / sizeof(KernelRow);
@@ -208,29 +209,57 @@ static bool hgemm_tma_ok(const GemmArgs& g) {
          g.ldc % 8 == 0 && g.k > 0;
 }
 
-template <int TM, int STAGES, bool AK, bool BK_>
+template <int TM, int STAGES, int CG, bool AK, bool BK_>
 static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                             const HgemmParams& p, unsigned grid, cudaStream_t st) {
-  using L = HgemmSmem<TM, STAGES>;
-  auto kern = hgemm_tcgen05_kernel<TM, STAGES, AK, BK_>;
+                             const HgemmParams& p, uint64_t tiles, cudaStream_t st) {
+  using L = HgemmSmem<TM, STAGES, CG>;
+  auto kern = hgemm_tcgen05_kernel<TM, STAGES, AK, BK_, CG>;
   static bool attr_done[kMaxDevices] = {};
+  static int max_walkers[kMaxDevices] = {};
   const int dev = current_device();
-  if (dev >= 0 && dev < kMaxDevices && !attr_done[dev]) {
+  if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
+  if (!attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return (int)e;
+    int walkers = sm_count() / CG;
+    if (CG == 2) {
+      // How many CTA pairs the device can hold at once (GPCs with an odd number of
+      // SMs leave one SM unpaired).
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3((unsigned)(2 * walkers));
+      q.blockDim = dim3(kHgemmThreads);
+      q.dynamicSmemBytes = L::kDynamic;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa; q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &q) == cudaSuccess && n > 0) walkers = n < walkers ? n : walkers;
+      else cudaGetLastError();
+    }
+    max_walkers[dev] = walkers;
     attr_done[dev] = true;
   }
-  kern<<<grid, kHgemmThreads, L::kDynamic, st>>>(ta, tb, tc, p);
-  return (int)cudaGetLastError();
+  const unsigned walkers = (unsigned)(tiles < (uint64_t)max_walkers[dev] ? tiles : (uint64_t)max_walkers[dev]);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(walkers * CG);
+  cfg.blockDim = dim3(kHgemmThreads);
+  cfg.dynamicSmemBytes = L::kDynamic;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
 }
 
-template <int TM, int STAGES>
+template <int TM, int STAGES, int CG>
 static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
   CUtensorMap ta, tb, tc;
   int rc;
   // op(A): K-major when transposed (stored k x m), MN-major otherwise (stored m x k).
   if (g.transA)
-    rc = make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.k, g.m, g.lda, kBlockK, TM);
+    rc = make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.k, g.m, g.lda, kBlockK, TM / CG);
   else
     rc = make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.m, g.k, g.lda, 64, kBlockK);
   if (rc) return rc;
@@ -246,16 +275,15 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   HgemmParams p;
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
   p.tiles_m = (uint32_t)((g.m + TM - 1) / TM);
-  p.tiles_n = (uint32_t)((g.n + kTileN - 1) / kTileN);
+  p.tiles_n = (uint32_t)((g.n + kTileN * CG - 1) / (kTileN * CG));
   p.wgm = wgm;
   p.alpha = g.alpha; p.beta = g.beta;
   const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
   if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-  const unsigned grid = (unsigned)(tiles < (uint64_t)sm_count() ? tiles : (uint64_t)sm_count());
-  if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, true, true>(ta, tb, tc, p, grid, st);
-  if (g.transA && g.transB) return launch_hgemm_inst<TM, STAGES, true, false>(ta, tb, tc, p, grid, st);
-  if (!g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, false, true>(ta, tb, tc, p, grid, st);
-  return launch_hgemm_inst<TM, STAGES, false, false>(ta, tb, tc, p, grid, st);
+  if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, true, true>(ta, tb, tc, p, tiles, st);
+  if (g.transA && g.transB) return launch_hgemm_inst<TM, STAGES, CG, true, false>(ta, tb, tc, p, tiles, st);
+  if (!g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, false, true>(ta, tb, tc, p, tiles, st);
+  return launch_hgemm_inst<TM, STAGES, CG, false, false>(ta, tb, tc, p, tiles, st);
 }
 
 // ------------------------------------------------------------------ selection --------
@@ -267,16 +295,23 @@ static int select_f32(const GemmArgs& g) {
 
 static int select_f16(const GemmArgs& g) {
   if (!hgemm_tma_ok(g)) return 0;
-  // Prefer the 256-wide tile unless the 128-wide one fills the SMs markedly better.
+  // Score = fraction of the machine kept busy over whole waves of tiles x relative
+  // speed of the kernel on a full wave (measured on 8192^3).
   const double sms = (double)sm_count();
-  auto eff = [&](uint64_t tiles) {
-    const double waves = (double)((tiles + (uint64_t)sms - 1) / (uint64_t)sms);
-    return (double)tiles / (waves * sms);
+  auto eff = [](uint64_t tiles, double walkers) {
+    const double waves = (double)((tiles + (uint64_t)walkers - 1) / (uint64_t)walkers);
+    return (double)tiles / (waves * walkers);
   };
-  const uint64_t t256 = (uint64_t)((g.m + 255) / 256) * ((g.n + 127) / 128);
-  const uint64_t t128 = (uint64_t)((g.m + 127) / 128) * ((g.n + 127) / 128);
-  if (g.m <= 128) return 2;
-  return eff(t256) >= 0.85 * eff(t128) ? 1 : 2;
+  const uint64_t t1 = (uint64_t)((g.m + 255) / 256) * ((g.n + 127) / 128);
+  const uint64_t t2 = (uint64_t)((g.m + 127) / 128) * ((g.n + 127) / 128);
+  const uint64_t t3 = (uint64_t)((g.m + 255) / 256) * ((g.n + 255) / 256);
+  // useful fraction of each tile (ragged edges waste tensor work)
+  auto fill = [&](uint64_t tiles, double tm, double tn) { return ((double)g.m * (double)g.n) / ((double)tiles * tm * tn); };
+  const double s1 = 0.80 * eff(t1, sms) * fill(t1, 256, 128);
+  const double s2 = 0.70 * eff(t2, sms) * fill(t2, 128, 128);
+  const double s3 = 1.00 * eff(t3, sms / 2) * fill(t3, 256, 256);
+  if (s3 >= s1 && s3 >= s2) return 3;
+  return s1 >= s2 ? 1 : 2;
 }
 
 static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
@@ -297,10 +332,13 @@ static int run_f16(const GemmArgs& g, int id, cudaStream_t st) {
     case 0: return launch_simple<__half>(g, st);
     case 1:
       if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
-      return launch_hgemm_tcgen05<256, 4>(g, env_u32("MMBO_WGM", kF16Rows[1].wgm), st);
+      return launch_hgemm_tcgen05<256, 4, 1>(g, env_u32("MMBO_WGM", kF16Rows[1].wgm), st);
     case 2:
       if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
-      return launch_hgemm_tcgen05<128, 6>(g, env_u32("MMBO_WGM", kF16Rows[2].wgm), st);
+      return launch_hgemm_tcgen05<128, 6, 1>(g, env_u32("MMBO_WGM", kF16Rows[2].wgm), st);
+    case 3:
+      if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
+      return launch_hgemm_tcgen05<256, 6, 2>(g, env_u32("MMBO_WGM", kF16Rows[3].wgm), st);
   }
   return MMBO_ERR_BAD_KERNEL_ID;
 }

@@ -74,12 +74,15 @@ def test_config2_hgemm_nt_8192(cuda, mm, oracle):
     torch.cuda.synchronize()
     d = (C.float() - Cs.float()).norm() / Cs.float().norm()
     assert float(d) <= 2e-3
-    # linearity in alpha with beta = 0: C(2a) == 2*C(a) exactly (power-of-two scaling)
+    # linearity in alpha with beta = 0: scaling alpha by two scales every result that
+    # is a normal fp16 number exactly (subnormal results round on a fixed grid instead)
     C1, C2 = torch.empty_like(C), torch.empty_like(C)
     mm.hgemm_NT(m, n, k, 0.25, A, ra, B, rb, 0.0, C1, m)
     mm.hgemm_NT(m, n, k, 0.5, A, ra, B, rb, 0.0, C2, m)
     torch.cuda.synchronize()
-    assert torch.equal(C1 * 2, C2)
+    normal = C1.abs() >= 2.0 ** -14
+    assert torch.equal((C1 * 2)[normal], C2[normal])
+    assert float((C1.float() * 2 - C2.float()).abs().max()) <= 2.0 ** -24
 
 
 @pytest.mark.parametrize("m,n,k", [(65536, 128, 4096), (128, 65536, 4096), (8192, 8192, 256)])

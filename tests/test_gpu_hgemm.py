@@ -9,12 +9,13 @@ pytestmark = pytest.mark.gpu
 
 MODES = [(False, False), (False, True), (True, False), (True, True)]
 # 0/1/several/partial tiles of the 256x128 and 128x128 macro-tiles; K tails of the
-# 64-deep stage; more tiles than stages and than accumulators
+# 64-deep stage; more tiles than stages and than accumulators; odd numbers of
+# 128-column blocks so that a CTA pair's second half falls outside C
 SHAPES = [(8, 8, 8), (64, 32, 16), (128, 128, 64), (256, 128, 128), (136, 72, 200), (264, 136, 72),
           (520, 392, 328), (1024, 512, 640), (40, 1000, 96), (1000, 40, 96)]
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, -1, 0])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, -1, 0])
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_hgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
     for (m, n, k) in SHAPES:
@@ -24,13 +25,13 @@ def test_hgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
             run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, -1, 0])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, -1, 0])
 def test_hgemm_beta_zero_never_reads_c(cuda, mm, oracle, kernel_id):
     case = Case(oracle, "f16", False, True, 264, 200, 72, 2.0, 0.0, pad=(0, 8, 16), c_poison=True)
     run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, -1])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, -1])
 def test_hgemm_many_tiles_per_cta(cuda, mm, oracle, kernel_id):
     """More tiles than SMs: every persistent CTA walks several tiles, so stage and
     accumulator phases wrap many times."""
