@@ -138,6 +138,7 @@ def cpu_panel_time(O, w, pm: int, pn: int, repeats: int = 1) -> float:
 
 def cpu_baseline(w, budget_s: float = 12.0):
     from oracle import oracle as O
+    O.set_num_threads(0)  # every host core, even when the launcher exported OMP_NUM_THREADS=1
     t = cpu_panel_time(O, w, 512, 512)
     rate = 2.0 * 512 * 512 * w["k"] / t  # flop/s
     # panel edge for ~budget_s of work, multiple of 256, within the problem
@@ -156,6 +157,7 @@ def run_reference(args, rank: int):
     if rank != 0:
         return
     from oracle import oracle as O
+    O.set_num_threads(0)  # every host core, even when the launcher exported OMP_NUM_THREADS=1
     w = workload(args.gpus, args.size)
     t_probe = cpu_panel_time(O, w, 512, 512)
     rate = 2.0 * 512 * 512 * w["k"] / t_probe
@@ -205,7 +207,7 @@ def main():
     P = world if world > 1 else 1
     w = workload(args.gpus if world == 1 else world, args.size)
     m, n, k, ta, tb = w["m"], w["n"], w["k"], w["ta"], w["tb"]
-    col0, ncols = mm.shard_columns(n, P, rank) if P > 1 else (0, n)
+    col0, ncols = mm.shard_columns(n, P, rank, 256) if P > 1 else (0, n)
 
     # Operands, generated on the device from the shared seeded generator.
     ra, rb = (k if ta else m), (ncols if tb else k)
@@ -221,10 +223,17 @@ def main():
     mm.fill("f16", C, m, ncols, m, mat=2, dist=w["dist"], scale=w["scale"], col0=col0, total_rows=m)
     Cfull = torch.empty((n, m), dtype=torch.float16, device="cuda") if (args.gather and P > 1) else None
 
+    shard = None
+    if Cfull is not None:
+        from gemm_mmbo_b200.sharded import ColumnShard
+        shard = ColumnShard(n, P, rank)
+
     def step():
-        mm.gemm("f16", ta, tb, m, ncols, k, w["alpha"], A, ra, B, rb, w["beta"], C, m, args.kernel)
-        if Cfull is not None:
-            dist.all_gather_into_tensor(Cfull.view(-1), C.view(-1))
+        if shard is not None:  # GEMM in column panels, each panel's all-gather overlapped
+            shard.gemm_and_gather("f16", ta, tb, m, k, w["alpha"], A, ra, B, rb, w["beta"], C, Cfull,
+                                  panels=4, kernelId=args.kernel)
+        else:
+            mm.gemm("f16", ta, tb, m, ncols, k, w["alpha"], A, ra, B, rb, w["beta"], C, m, args.kernel)
 
     def barrier():
         if dist is not None:

@@ -1,0 +1,115 @@
+"""Column-block sharding of one large GEMM over the GPUs of a node.
+
+The contraction needs no communication: rank r owns columns [col0, col0 + ncols) of
+op(B) and of C, every rank holds all of A, and each rank runs an independent
+m x ncols x k GEMM through the library's C ABI.  The only exchange step is optional:
+reassembling the full C on every rank with an all-gather of the column blocks (NCCL
+over NVLink when the tensors are on GPUs).  The reference has no multi-device path
+(device index hard-coded: src/gemm/benchmark.cc:54); this is new capability behind
+the same GEMM call.
+
+One process per GPU; torch.distributed provides the process group.
+"""
+from __future__ import annotations
+
+import importlib
+from dataclasses import dataclass
+
+# the package re-exports a function called `gemm`, which hides the submodule attribute
+_g = importlib.import_module(__package__ + ".gemm")
+
+
+@dataclass(frozen=True)
+class ColumnShard:
+    """Partition of the n columns of op(B)/C among `world` ranks."""
+    n: int
+    world: int
+    rank: int
+    align: int = 256
+
+    @property
+    def col0(self) -> int:
+        return _g.shard_columns(self.n, self.world, self.rank, self.align)[0]
+
+    @property
+    def ncols(self) -> int:
+        return _g.shard_columns(self.n, self.world, self.rank, self.align)[1]
+
+    def block_of(self, rank: int) -> tuple[int, int]:
+        return _g.shard_columns(self.n, self.world, rank, self.align)
+
+    def blocks(self) -> list[tuple[int, int]]:
+        return [self.block_of(r) for r in range(self.world)]
+
+    # ---- operand placement -----------------------------------------------------------
+    def b_window(self, transB: bool, k: int) -> dict:
+        """Arguments for `gemm.fill` that generate this rank's block of B in place:
+        a column window when B is stored k x n, a row window when stored n x k."""
+        if transB:
+            return dict(rows=self.ncols, cols=k, row0=self.col0, col0=0, total_rows=self.n)
+        return dict(rows=k, cols=self.ncols, row0=0, col0=self.col0, total_rows=k)
+
+    # ---- compute -----------------------------------------------------------------------
+    def local_gemm(self, dtype, transA, transB, m, k, alpha, A, lda, B_block, ldb, beta, C_block, ldc,
+                   kernelId=_g.KERNEL_AUTO, stream=None, col_begin: int = 0, col_count: int | None = None):
+        """GEMM on this rank's block (or on columns [col_begin, col_begin + col_count) of it).
+        B_block is this rank's part of B: k x ncols (ldb >= k) when transB is false, ncols x k
+        (ldb >= ncols) when true; C_block is m x ncols."""
+        cnt = self.ncols - col_begin if col_count is None else col_count
+        if cnt <= 0:
+            return
+        esz = 4 if dtype in ("f32", _g.DTYPE_F32) else 2
+        b_off = (col_begin if transB else col_begin * ldb) * esz
+        c_off = col_begin * ldc * esz
+        _g.gemm(dtype, transA, transB, m, cnt, k, alpha, A, lda, _g._addr(B_block) + b_off, ldb, beta,
+                _g._addr(C_block) + c_off, ldc, kernelId, stream)
+
+    # ---- exchange ------------------------------------------------------------------------
+    def gather(self, C_block, C_full, m: int, group=None, col_begin: int = 0, col_count: int | None = None,
+               async_op: bool = False):
+        """All-gather columns [col_begin, col_begin + col_count) of every rank's block into the
+        full column-major C (shape (n, m), leading dimension m).  All blocks must have the
+        same width.  Works on any backend (NCCL for CUDA tensors, gloo for CPU tensors)."""
+        import torch.distributed as dist
+        widths = {nc for _, nc in self.blocks()}
+        if len(widths) != 1:
+            raise ValueError("gather needs equal column blocks; choose n divisible by world * align")
+        cnt = self.ncols - col_begin if col_count is None else col_count
+        outs = [C_full[c0 + col_begin:c0 + col_begin + cnt] for c0, _ in self.blocks()]
+        src = C_block[col_begin:col_begin + cnt]
+        if cnt == self.ncols and col_begin == 0 and C_full.is_contiguous():
+            return dist.all_gather_into_tensor(C_full.view(-1), src.reshape(-1), group=group, async_op=async_op)
+        return dist.all_gather(outs, src.contiguous(), group=group, async_op=async_op)
+
+    def gemm_and_gather(self, dtype, transA, transB, m, k, alpha, A, lda, B_block, ldb, beta, C_block, C_full,
+                        panels: int = 4, kernelId=_g.KERNEL_AUTO, group=None):
+        """Local GEMM in `panels` column panels; the all-gather of panel p runs on a side
+        stream while panel p+1 is being computed.  CUDA tensors, NCCL group."""
+        import torch
+        compute = torch.cuda.current_stream()
+        comm = _side_stream()
+        step = -(-self.ncols // panels)
+        step = -(-step // self.align) * self.align if step > self.align else step
+        begin = 0
+        while begin < self.ncols:
+            cnt = min(step, self.ncols - begin)
+            self.local_gemm(dtype, transA, transB, m, k, alpha, A, lda, B_block, ldb, beta, C_block, m, kernelId,
+                            compute, begin, cnt)
+            done = torch.cuda.Event()
+            done.record(compute)
+            comm.wait_event(done)
+            with torch.cuda.stream(comm):
+                self.gather(C_block, C_full, m, group, begin, cnt)
+            begin += cnt
+        compute.wait_stream(comm)
+
+
+_SIDE = {}
+
+
+def _side_stream():
+    import torch
+    dev = torch.cuda.current_device()
+    if dev not in _SIDE:
+        _SIDE[dev] = torch.cuda.Stream()
+    return _SIDE[dev]

@@ -60,6 +60,8 @@ def lib() -> ctypes.CDLL:
             f.argtypes = [_vp, _sz, _sz, _sz, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int,
                           ctypes.c_float, _sz, _sz, _sz]
         L.oracle_num_threads.restype = ctypes.c_int
+        L.oracle_set_num_threads.restype = None
+        L.oracle_set_num_threads.argtypes = [ctypes.c_int]
         L.oracle_wgm_map_grid.restype = None
         L.oracle_wgm_map_grid.argtypes = [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, _vp]
         u32p = ctypes.POINTER(ctypes.c_uint32)
@@ -137,6 +139,11 @@ def wgm_unmap(m0: int, m1: int, nwg0: int, nwg1: int, wgm: int) -> tuple[int, in
     a, b = ctypes.c_uint32(), ctypes.c_uint32()
     lib().oracle_wgm_unmap(m0, m1, nwg0, nwg1, wgm, ctypes.byref(a), ctypes.byref(b))
     return a.value, b.value
+
+
+def set_num_threads(n: int = 0) -> None:
+    """n <= 0: one thread per host core, whatever OMP_NUM_THREADS says."""
+    lib().oracle_set_num_threads(int(n))
 
 
 def num_threads() -> int:

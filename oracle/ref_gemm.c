@@ -235,6 +235,17 @@ void oracle_fill_f16(uint16_t *dst, size_t rows, size_t cols, size_t ld, uint64_
           mmbo_rng_value(seed, mat, row0 + i, col0 + (size_t)j, total_rows, dist, scale));
 }
 
+/* Thread count for the parallel loops (launchers such as torchrun export
+ * OMP_NUM_THREADS=1; the CPU baseline wants every host core).  n <= 0: all cores. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n <= 0) n = omp_get_num_procs();
+  omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

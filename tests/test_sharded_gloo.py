@@ -1,0 +1,81 @@
+"""Host-side logic of the multi-GPU path on CPU ranks (gloo, world size 2): the column
+partition tiles the matrix, every rank's operand window reproduces the matching slice
+of the whole matrix, and the gather of the C blocks (whole block and panel by panel)
+reassembles the full column-major C."""
+import os
+import socket
+import sys
+import pathlib
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, n: int, m: int, k: int, q):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from gemm_mmbo_b200.sharded import ColumnShard
+        from oracle import oracle as O
+        sh = ColumnShard(n, world, rank, align=64)
+        blocks = sh.blocks()
+        assert blocks[0][0] == 0 and sum(nc for _, nc in blocks) == n
+        assert all(blocks[i][0] + blocks[i][1] == blocks[i + 1][0] for i in range(world - 1))
+        # operand windows: this rank's block of B equals the slice of the whole B
+        for tb in (False, True):
+            w = sh.b_window(tb, k)
+            whole = O.fill("f16", n if tb else k, k if tb else n, mat=O.MAT_B)
+            mine = O.fill("f16", w["rows"], w["cols"], mat=O.MAT_B, row0=w["row0"], col0=w["col0"],
+                          total_rows=w["total_rows"])
+            want = whole[:, sh.col0:sh.col0 + sh.ncols] if tb else whole[sh.col0:sh.col0 + sh.ncols]
+            assert np.array_equal(mine.view(np.uint16), want.view(np.uint16))
+        # exchange: blocks of a known full C
+        full = O.fill("f16", m, n, mat=O.MAT_C)                     # (n, m)
+        mine = torch.from_numpy(full[sh.col0:sh.col0 + sh.ncols].copy())
+        out = torch.zeros((n, m), dtype=torch.float16)
+        sh.gather(mine, out, m)
+        assert np.array_equal(out.numpy().view(np.uint16), full.view(np.uint16))
+        out2 = torch.zeros((n, m), dtype=torch.float16)
+        step = 64
+        for b in range(0, sh.ncols, step):
+            sh.gather(mine, out2, m, col_begin=b, col_count=min(step, sh.ncols - b))
+        assert np.array_equal(out2.numpy().view(np.uint16), full.view(np.uint16))
+        q.put((rank, "ok"))
+    except Exception as e:  # report instead of hanging the peer
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(180)
+def test_two_cpu_ranks_partition_and_gather():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 512, 96, 40, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=150) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+    assert results == {0: "ok", 1: "ok"}, results
+
+
+def test_unequal_blocks_refuse_gather():
+    sys.path.insert(0, str(ROOT))
+    from gemm_mmbo_b200.sharded import ColumnShard
+    sh = ColumnShard(1000, 3, 0, align=128)
+    with pytest.raises(ValueError):
+        sh.gather(torch.zeros((sh.ncols, 8)), torch.zeros((1000, 8)), 8)
