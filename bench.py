@@ -279,8 +279,12 @@ def main():
     # seconds, burst otherwise
     peak = peaks["sustained"] if ms > 2000.0 else peaks["burst"]
     achieved = 2.0 * m * ncols * k / (kern_avg * 1e-3) / 1e12
+    # DRAM bytes per launch from the ncu capture of this workload (dram__bytes_read.sum +
+    # dram__bytes_write.sum; summary under profiles/): known for the default N=1 case only
+    traffic = 1.377e9 if (P == 1 and (m, n, k) == (8192, 8192, 8192) and args.kernel in (-1, 3)) else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None,
+                "frac": achieved / peak, "traffic": traffic,
+                "algorithmic_bytes": 2.0 * (m * k + k * ncols + m * ncols * (2 if w["beta"] else 1)),
                 "peak_source": f"{peaks['source']} cuBLAS bf16 "
                                f"({'sustained' if ms > 2000.0 else 'burst'}); nominal dense fp16 2250",
                 "frac_of_nominal": achieved / 2250.0,

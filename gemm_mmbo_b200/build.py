@@ -68,9 +68,9 @@ def build_harness(force: bool = False) -> list[pathlib.Path]:
         if not force and _newer(exe, [src, LIB, *sorted((ROOT / "include").glob("*.h*"))]):
             out.append(exe)
             continue
-        cmd = [_nvcc(), "-x", "cu", *NVCC_FLAGS, "-Xcompiler", "-fopenmp", "-I", str(ROOT / "include"),
-               "-o", str(exe), str(src), f"-L{BUILD}", "-lmmbo_gemm", "-lcudart", "-lgomp",
-               f"-Xlinker=-rpath={BUILD}"]
+        cmd = [_nvcc(), "-x", "cu", *NVCC_FLAGS, "-I", str(ROOT / "include"),
+               "-o", str(exe), str(src), f"-L{BUILD}", "-lmmbo_gemm", "-lcudart", "-lcublas",
+               "-Xlinker", "-rpath=$ORIGIN"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"nvcc failed for {name}:\n{res.stdout}\n{res.stderr}")

@@ -22,8 +22,14 @@ _vp = ctypes.c_void_p
 
 def build(force: bool = False) -> pathlib.Path:
     """Compile the oracle with the Makefile beside this file (gcc only)."""
-    if force or not _LIB_PATH.exists():
+    if force and _LIB_PATH.exists():
+        _LIB_PATH.unlink()
+    # make rebuilds only when a source is newer than the library
+    try:
         subprocess.run(["make", "-C", str(_HERE), "all"], check=True, capture_output=True)
+    except (OSError, subprocess.CalledProcessError):
+        if not _LIB_PATH.exists():  # a prebuilt library is used as it is
+            raise
     return _LIB_PATH
 
 

@@ -131,3 +131,33 @@ def test_config5_hgemm_nn_32768_one_shard(cuda, mm, oracle):
     err = np.linalg.norm(got - want) / np.linalg.norm(want)
     assert err <= TOL["f16"], err
     assert torch.isfinite(C).all()
+
+
+def _harness(name):
+    import pathlib
+    exe = pathlib.Path(__file__).resolve().parents[1] / "gemm_mmbo_b200" / "_build" / name
+    if not exe.exists():
+        pytest.skip(f"{name} not built")
+    return str(exe)
+
+
+def test_cpp_harness_test_program(cuda):
+    """The C++ test program (counterpart of the reference's test.cc) on the reference's
+    default HPL shape and on an fp32 ragged shape; exit code 0 = matches cuBLAS and kernel 0."""
+    import subprocess
+    for argv in ([], ["4095", "4097", "1023", "--dtype", "f32", "--trans", "TN", "--alpha", "1.5", "--beta", "-0.25"]):
+        r = subprocess.run([_harness("test_gemm"), *argv], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stdout + r.stderr
+        assert "results match" in r.stdout
+
+
+def test_cpp_harness_benchmark_program(cuda):
+    """The C++ benchmark in the reference's positional form, all three arms."""
+    import re
+    import subprocess
+    for typ in ("0", "1", "2"):
+        r = subprocess.run([_harness("benchmark"), typ, "4224", "2048", "384", "4224", "2048", "4224"],
+                           capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stdout + r.stderr
+        m = re.search(r"time, tflops, efficiency = .*?([0-9.]+), ([0-9.]+), ([0-9.]+)%", r.stdout)
+        assert m and float(m.group(2)) > 0.0, r.stdout
