@@ -2,9 +2,26 @@
 
 The library itself is CUDA C++ (gemm_mmbo_b200/csrc, C ABI in include/mmbo_gemm.h); this
 package only binds it for Python callers (tests, benchmark, multi-GPU driver).
+
+The binding is loaded on first use of any public name, so that `gemm_mmbo_b200.build`
+can be imported to (re)build the library.  There is no fallback: touching any GEMM
+entry point without a built libmmbo_gemm.so raises ImportError.
 """
-from .gemm import (  # noqa: F401
-    DTYPE_F16, DTYPE_F32, KERNEL_AUTO, MmboError, device_status, fill, gemm, hgemm_NN, hgemm_NT,
-    hgemm_TN, hgemm_TT, kernel_name, kernel_params, kernel_table, num_kernels, select_kernel,
-    sgemm_NN, sgemm_NT, sgemm_TN, sgemm_TT, shard_columns, status_string, wgm_map,
+import importlib
+
+_PUBLIC = (
+    "DTYPE_F16", "DTYPE_F32", "KERNEL_AUTO", "DIST_UNIFORM", "DIST_NORMAL", "DIST_ZERO", "MAT_A", "MAT_B",
+    "MAT_C", "MmboError", "device_status", "fill", "gemm", "hgemm_NN", "hgemm_NT", "hgemm_TN", "hgemm_TT",
+    "kernel_name", "kernel_params", "kernel_table", "num_kernels", "select_kernel", "sgemm_NN", "sgemm_NT",
+    "sgemm_TN", "sgemm_TT", "shard_columns", "status_string", "wgm_map", "workspace_bytes", "set_workspace",
 )
+__all__ = list(_PUBLIC)
+
+
+def __getattr__(name):
+    if name in _PUBLIC:
+        mod = importlib.import_module(__name__ + ".gemm")  # loads libmmbo_gemm.so or raises
+        for n in _PUBLIC:
+            globals()[n] = getattr(mod, n)
+        return globals()[name]
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

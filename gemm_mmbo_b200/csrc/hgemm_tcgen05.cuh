@@ -25,11 +25,14 @@
 //   * Epilogue: tcgen05.ld -> alpha*acc (+ beta*C, with C fetched by TMA into the same
 //     staging buffer; beta == 0 never reads C, src/gemm/ref/Kernels.cpp:87) -> fp16 ->
 //     swizzled staging -> TMA store, per warp, double buffered.
-//   * Ragged M, N, K need no special code: TMA zero-fills out-of-range loads and clips
-//     out-of-range stores.
+//   * Ragged M, N, K need no special code on the load side: TMA zero-fills out-of-range
+//     loads.  TMA stores clip out-of-range elements in units of 16 bytes, so C goes
+//     through TMA only when m is a multiple of 8 (and C is 16-byte aligned with
+//     ldc % 8 == 0); otherwise the epilogue writes its staging tile with coalesced plain
+//     stores (and reads the old C the same way).
 //
-// Requirements checked by the host before choosing this kernel: 16-byte aligned base
-// pointers and leading dimensions that are multiples of 8 elements (TMA strides).
+// Requirements checked by the host before choosing this kernel: A and B have 16-byte
+// aligned bases and leading dimensions that are multiples of 8 elements (TMA strides).
 #pragma once
 
 #include <cuda_fp16.h>
@@ -70,6 +73,11 @@ struct HgemmParams {
   uint32_t tiles_m, tiles_n;  // ceil(m / TM), ceil(n / (128 * CG))
   uint32_t wgm;               // work-group-mapping width (tile columns per block)
   float alpha, beta;
+  __half* c;       // C and its leading dimension, for the epilogue without TMA
+  uint32_t ldc;
+  uint32_t c_tma;  // 1: C goes through the tensor map (16-byte aligned base, ldc % 8 == 0,
+                   // m % 8 == 0: TMA stores whole 16-byte units, so a ragged m would spill
+                   // into the padding rows below the matrix)
 };
 
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
@@ -131,7 +139,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     fence_mbar_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
-    prefetch_tensormap(&tmap_c);
+    if (p.c_tma) prefetch_tensormap(&tmap_c);
   }
   __syncwarp();
   if (warp == 1) {
@@ -268,6 +276,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t buf_base = smem_base + L::kEpiOffset + epi_w * 2u * kEpiBufBytes;
     uint8_t* buf_gen = smem_gen + L::kEpiOffset + epi_w * 2u * kEpiBufBytes;
     const bool use_c = (p.beta != 0.0f);
+    const bool c_tma = p.c_tma != 0u;
     const float alpha = p.alpha, beta = p.beta;
     uint32_t local_tile = 0, chunk_ctr = 0;
     uint32_t cphase[2] = {0u, 0u};
@@ -293,18 +302,40 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint8_t* gbuf = buf_gen + b * kEpiBufBytes;
         const uint32_t mrow0 = m0 + 64u * c;
         const bool in_range = (mrow0 < p.m) && (ncol0 < p.n);  // warp-uniform
-        // The store issued from this buffer two chunks ago must have read it.
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
         const bool load_c = use_c && in_range;
-        if (load_c && lane == 0) {
-          mbar_expect_tx(cload_bar(epi_w, b), kEpiBufBytes);
-          tma_load_2d(sbuf, &tmap_c, cload_bar(epi_w, b), static_cast<int32_t>(mrow0),
-                      static_cast<int32_t>(ncol0));
+        // Staging tile: row t = C column ncol0 + t, 64 fp16 = rows mrow0 .. mrow0+63; the
+        // 16-byte piece j of a row lives at piece j ^ (t & 7) (the 128-byte TMA swizzle).
+        if (c_tma) {
+          // The store issued from this buffer two chunks ago must have read it.
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          if (load_c && lane == 0) {
+            mbar_expect_tx(cload_bar(epi_w, b), kEpiBufBytes);
+            tma_load_2d(sbuf, &tmap_c, cload_bar(epi_w, b), static_cast<int32_t>(mrow0),
+                        static_cast<int32_t>(ncol0));
+          }
+        } else {
+          __syncwarp();  // the previous plain write-out of this buffer is complete
+          if (load_c) {
+            // coalesced read of the old C: lanes run along the rows of the chunk
+            __half* hb = reinterpret_cast<__half*>(gbuf);
+#pragma unroll 2
+            for (uint32_t t = 0; t < 32; ++t) {
+              const uint32_t nj = ncol0 + t;
+#pragma unroll
+              for (uint32_t hh = 0; hh < 2; ++hh) {
+                const uint32_t i = lane + 32u * hh, mi = mrow0 + i;
+                __half v = __float2half_rn(0.f);
+                if (mi < p.m && nj < p.n) v = p.c[(size_t)mi + (size_t)nj * p.ldc];
+                hb[t * 64u + ((((i >> 3) ^ (t & 7u)) << 3) | (i & 7u))] = v;
+              }
+            }
+            __syncwarp();
+          }
         }
         uint32_t r[32];
         tmem_ld_32x32(t_warp + 64u * c, r);
-        if (load_c) {
+        if (c_tma && load_c) {
           if (!mbar_wait(cload_bar(epi_w, b), cphase[b], abort_flag, kFaultWaitCLoad, epi_w)) ok = false;
           cphase[b] ^= 1u;
         }
@@ -347,12 +378,29 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             *reinterpret_cast<uint4*>(addr) = out;
           }
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (in_range && ok)
-            tma_store_2d(&tmap_c, sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
-          tma_store_commit();
+        if (c_tma) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (in_range && ok)
+              tma_store_2d(&tmap_c, sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
+            tma_store_commit();
+          }
+        } else {
+          __syncwarp();
+          if (in_range) {
+            const __half* hb = reinterpret_cast<const __half*>(gbuf);
+#pragma unroll 2
+            for (uint32_t t = 0; t < 32; ++t) {
+              const uint32_t nj = ncol0 + t;
+#pragma unroll
+              for (uint32_t hh = 0; hh < 2; ++hh) {
+                const uint32_t i = lane + 32u * hh, mi = mrow0 + i;
+                const __half v = hb[t * 64u + ((((i >> 3) ^ (t & 7u)) << 3) | (i & 7u))];
+                if (mi < p.m && nj < p.n) p.c[(size_t)mi + (size_t)nj * p.ldc] = v;
+              }
+            }
+          }
         }
         ok = __all_sync(0xffffffffu, ok);
       }

@@ -14,6 +14,7 @@
 #include "hgemm_tcgen05.cuh"
 #include "ref_kernels.cuh"
 #include "sgemm_ffma.cuh"
+#include "sgemm_tf32x3.cuh"
 
 namespace mmbo {
 
@@ -29,6 +30,8 @@ static const KernelRow kF32Rows[] = {
     {"sgemm_simple_MT032x008x01_TT01_01_WG256", 32, 8, 256, 1, 1, 1, 1, 0},
     {"sgemm_ffma_MT128x128x16_TT08_08_WG256_WGM08", 128, 128, 256, 16, 2, 1, 8, 0},
     {"sgemm_ffma_MT064x064x16_TT04_04_WG256_WGM08", 64, 64, 256, 16, 2, 1, 8, 0},
+    {"sgemm_tf32x3_tcgen05_MT128x256x32_S4_CG2_WG192_WGM08", 128, 256, 192, 32, 4, 2, 8, 1},
+    {"sgemm_tf32x3_tcgen05_MT128x128x32_S3_CG1_WG192_WGM08", 128, 128, 192, 32, 3, 1, 8, 1},
 };
 // fp16 rows: MT<tile m>x<tile n>x<DepthU>_S<stages>_CG<cta group>.
 static const KernelRow kF16Rows[] = {
@@ -205,8 +208,7 @@ static int launch_sgemm_ffma(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
 // The tcgen05 kernel addresses its operands through TMA: 16-byte aligned bases and
 // leading dimensions that are multiples of 8 fp16 elements.
 static bool hgemm_tma_ok(const GemmArgs& g) {
-  return aligned16(g.A) && aligned16(g.B) && aligned16(g.C) && g.lda % 8 == 0 && g.ldb % 8 == 0 &&
-         g.ldc % 8 == 0 && g.k > 0;
+  return aligned16(g.A) && aligned16(g.B) && g.lda % 8 == 0 && g.ldb % 8 == 0 && g.k > 0;
 }
 
 template <int TM, int STAGES, int CG, bool AK, bool BK_>
@@ -269,8 +271,14 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   else
     rc = make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.B, g.n, g.k, g.ldb, 64, kBlockK);
   if (rc) return rc;
-  rc = make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.C, g.m, g.n, g.ldc, 64, 32);
-  if (rc) return rc;
+  // C through TMA only when whole 16-byte units stay inside the matrix (see HgemmParams).
+  const bool c_tma = aligned16(g.C) && g.ldc % 8 == 0 && g.m % 8 == 0;
+  if (c_tma) {
+    rc = make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.C, g.m, g.n, g.ldc, 64, 32);
+    if (rc) return rc;
+  } else {
+    tc = ta;  // placeholder, never dereferenced by the plain epilogue
+  }
 
   HgemmParams p;
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
@@ -278,6 +286,7 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   p.tiles_n = (uint32_t)((g.n + kTileN * CG - 1) / (kTileN * CG));
   p.wgm = wgm;
   p.alpha = g.alpha; p.beta = g.beta;
+  p.c = static_cast<__half*>(g.C); p.ldc = (uint32_t)g.ldc; p.c_tma = c_tma ? 1u : 0u;
   const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
   if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
   if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, true, true>(ta, tb, tc, p, tiles, st);
@@ -286,9 +295,160 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   return launch_hgemm_inst<TM, STAGES, CG, false, false>(ta, tb, tc, p, tiles, st);
 }
 
+// ------------------------------------------------------------------ scratch memory --
+// One scratch buffer per device, used by the kernels that repack operands (the
+// 3xTF32 SGEMM).  Either the caller lends one (mmbo_set_workspace) or the library grows
+// its own on demand.  Calls that use scratch and overlap on the GPU (different streams)
+// would race on it: such callers lend a buffer per stream and serialise per buffer.
+struct Workspace {
+  void* ptr;
+  size_t bytes;
+  bool user;
+};
+static Workspace g_ws[kMaxDevices];
+
+static int ensure_workspace(size_t bytes, void** out) {
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
+  Workspace& w = g_ws[dev];
+  if (w.bytes < bytes) {
+    if (w.user) return MMBO_ERR_WORKSPACE;
+    if (w.ptr) {
+      cudaError_t e = cudaFree(w.ptr);  // waits for the kernels still using it
+      w.ptr = nullptr;
+      w.bytes = 0;
+      if (e != cudaSuccess) return (int)e;
+    }
+    cudaError_t e = cudaMalloc(&w.ptr, bytes);
+    if (e != cudaSuccess) {
+      w.ptr = nullptr;
+      return (int)e;
+    }
+    w.bytes = bytes;
+  }
+  *out = w.ptr;
+  return MMBO_OK;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Scratch layout of the 3xTF32 SGEMM: A_hi, A_lo (m rows of Kpad floats), B_hi, B_lo (n rows).
+struct Tf32Scratch {
+  size_t kpad, a_bytes, b_bytes, total;
+};
+static Tf32Scratch tf32_scratch(size_t m, size_t n, size_t k) {
+  Tf32Scratch s;
+  s.kpad = align_up(k, 32);
+  s.a_bytes = align_up(m * s.kpad * 4, 1024);
+  s.b_bytes = align_up(n * s.kpad * 4, 1024);
+  s.total = 2 * (s.a_bytes + s.b_bytes);
+  return s;
+}
+
+template <int TM, int STAGES, int CG>
+static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float* a_lo, const float* b_hi,
+                              const float* b_lo, size_t kpad, uint32_t wgm, cudaStream_t st) {
+  using L = TfSmem<TM, STAGES, CG>;
+  auto kern = sgemm_tf32x3_kernel<TM, STAGES, CG>;
+  CUtensorMap ta_hi, ta_lo, tb_hi, tb_lo, tc;
+  int rc;
+  if ((rc = make_map_2d(&ta_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a_hi, g.k, g.m, kpad, kTfBlockK, TM / CG))) return rc;
+  if ((rc = make_map_2d(&ta_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a_lo, g.k, g.m, kpad, kTfBlockK, TM / CG))) return rc;
+  if ((rc = make_map_2d(&tb_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b_hi, g.k, g.n, kpad, kTfBlockK, kTfTileN))) return rc;
+  if ((rc = make_map_2d(&tb_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b_lo, g.k, g.n, kpad, kTfBlockK, kTfTileN))) return rc;
+  // TMA stores whole 16-byte units: only when m is a multiple of 4 floats do they stay
+  // inside the matrix.
+  const bool c_tma = aligned16(g.C) && g.ldc % 4 == 0 && g.m % 4 == 0;
+  if (c_tma) {
+    if ((rc = make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.C, g.m, g.n, g.ldc, 32, 32))) return rc;
+  } else {
+    tc = ta_hi;  // placeholder, never dereferenced by the plain epilogue
+  }
+  TfParams p;
+  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
+  p.tiles_m = (uint32_t)((g.m + TM - 1) / TM);
+  p.tiles_n = (uint32_t)((g.n + kTfTileN * CG - 1) / (kTfTileN * CG));
+  p.wgm = wgm; p.alpha = g.alpha; p.beta = g.beta;
+  p.c = static_cast<float*>(g.C); p.ldc = (uint32_t)g.ldc; p.c_tma = c_tma ? 1u : 0u;
+  p.chunk = env_u32("MMBO_TF32_CHUNK", 4);
+  if (p.chunk == 0) p.chunk = 1;
+  const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
+  if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
+
+  static bool attr_done[kMaxDevices] = {};
+  static int max_walkers[kMaxDevices] = {};
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
+  if (!attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess) return (int)e;
+    int walkers = sm_count() / CG;
+    if (CG == 2) {
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3((unsigned)(2 * walkers));
+      q.blockDim = dim3(kTfThreads);
+      q.dynamicSmemBytes = L::kDynamic;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa; q.numAttrs = 1;
+      int nmax = 0;
+      if (cudaOccupancyMaxActiveClusters(&nmax, kern, &q) == cudaSuccess && nmax > 0) walkers = nmax < walkers ? nmax : walkers;
+      else cudaGetLastError();
+    }
+    max_walkers[dev] = walkers;
+    attr_done[dev] = true;
+  }
+  const unsigned walkers = (unsigned)(tiles < (uint64_t)max_walkers[dev] ? tiles : (uint64_t)max_walkers[dev]);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(walkers * CG);
+  cfg.blockDim = dim3(kTfThreads);
+  cfg.dynamicSmemBytes = L::kDynamic;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, ta_hi, ta_lo, tb_hi, tb_lo, tc, p);
+}
+
+// Split + repack of both operands into `scratch`, then the tensor-core GEMM.
+template <int TM, int STAGES, int CG>
+static int run_tf32x3(const GemmArgs& g, void* scratch, uint32_t wgm, cudaStream_t st) {
+  const Tf32Scratch s = tf32_scratch(g.m, g.n, g.k);
+  if (((g.m + 31) / 32) > 65535 || ((g.n + 31) / 32) > 65535) return MMBO_ERR_TOO_LARGE;
+  char* base = static_cast<char*>(scratch);
+  float* a_hi = reinterpret_cast<float*>(base);
+  float* a_lo = reinterpret_cast<float*>(base + s.a_bytes);
+  float* b_hi = reinterpret_cast<float*>(base + 2 * s.a_bytes);
+  float* b_lo = reinterpret_cast<float*>(base + 2 * s.a_bytes + s.b_bytes);
+  const dim3 block(32, 8);
+  const dim3 grid_a((unsigned)((g.k + 31) / 32), (unsigned)((g.m + 31) / 32));
+  const dim3 grid_b((unsigned)((g.k + 31) / 32), (unsigned)((g.n + 31) / 32));
+  const float* A = static_cast<const float*>(g.A);
+  const float* B = static_cast<const float*>(g.B);
+  // op(A)(i,l): row index contiguous unless transposed; op(B)(l,j) as an n x k operand:
+  // row index contiguous when transposed.
+  if (!g.transA) split_pack_kernel<true><<<grid_a, block, 0, st>>>(A, g.lda, (uint32_t)g.m, (uint32_t)g.k, (uint32_t)s.kpad, a_hi, a_lo);
+  else split_pack_kernel<false><<<grid_a, block, 0, st>>>(A, g.lda, (uint32_t)g.m, (uint32_t)g.k, (uint32_t)s.kpad, a_hi, a_lo);
+  if (g.transB) split_pack_kernel<true><<<grid_b, block, 0, st>>>(B, g.ldb, (uint32_t)g.n, (uint32_t)g.k, (uint32_t)s.kpad, b_hi, b_lo);
+  else split_pack_kernel<false><<<grid_b, block, 0, st>>>(B, g.ldb, (uint32_t)g.n, (uint32_t)g.k, (uint32_t)s.kpad, b_hi, b_lo);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  return launch_tf32x3_gemm<TM, STAGES, CG>(g, a_hi, a_lo, b_hi, b_lo, s.kpad, wgm, st);
+}
+
 // ------------------------------------------------------------------ selection --------
 static int select_f32(const GemmArgs& g) {
   if (g.k == 0) return 0;
+  // The split-precision tensor-core kernels hold the fp32 tolerance and are several
+  // times faster than the FFMA pipe once the three launches they need are amortised.
+  // MMBO_F32_EXACT=1 keeps automatic selection on the CUDA-core kernels.
+  const double work = (double)g.m * (double)g.n * (double)g.k;
+  if (work >= 512.0 * 512.0 * 512.0 && env_u32("MMBO_F32_EXACT", 0) == 0) {
+    const uint64_t pair_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 255) / 256);
+    return pair_tiles >= (uint64_t)(sm_count() / 2) ? 3 : 4;
+  }
   const uint64_t big_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 127) / 128);
   return big_tiles >= 2ull * (uint64_t)sm_count() ? 1 : 2;
 }
@@ -321,6 +481,14 @@ static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
     case 0: return launch_simple<float>(g, st);
     case 1: return launch_sgemm_ffma<128, 128, 8, 8>(g, env_u32("MMBO_WGM", kF32Rows[1].wgm), st);
     case 2: return launch_sgemm_ffma<64, 64, 4, 4>(g, env_u32("MMBO_WGM", kF32Rows[2].wgm), st);
+    case 3:
+    case 4: {
+      void* scratch = nullptr;
+      const int rc = ensure_workspace(tf32_scratch(g.m, g.n, g.k).total, &scratch);
+      if (rc) return rc;
+      if (id == 3) return run_tf32x3<128, 4, 2>(g, scratch, env_u32("MMBO_WGM", kF32Rows[3].wgm), st);
+      return run_tf32x3<128, 3, 1>(g, scratch, env_u32("MMBO_WGM", kF32Rows[4].wgm), st);
+    }
   }
   return MMBO_ERR_BAD_KERNEL_ID;
 }
@@ -429,6 +597,7 @@ const char* mmbo_status_string(int status) {
     case MMBO_ERR_TENSOR_MAP: return "tensor map rejected by the driver";
     case MMBO_ERR_DEVICE_FAULT: return "a kernel recorded a bounded-wait time-out";
     case MMBO_ERR_TOO_LARGE: return "problem exceeds launch limits of the chosen kernel";
+    case MMBO_ERR_WORKSPACE: return "the workspace lent by the caller is too small for this call";
   }
   if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
   return "unknown status";
@@ -482,6 +651,31 @@ int mmbo_fill_f32(float* dst, size_t rows, size_t cols, size_t ld, uint64_t seed
 int mmbo_fill_f16(void* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat, int dist,
                   float scale, size_t row0, size_t col0, size_t total_rows, void* stream) {
   return fill_common(MMBO_DTYPE_F16, dst, rows, cols, ld, seed, mat, dist, scale, row0, col0, total_rows, stream);
+}
+
+int mmbo_gemm_workspace_bytes(int dtype, int kernelId, size_t m, size_t n, size_t k, size_t* bytes) {
+  if (!bytes) return MMBO_ERR_NULL_POINTER;
+  int count = 0;
+  if (!rows_of(dtype, &count)) return MMBO_ERR_BAD_DTYPE;
+  if (kernelId < 0 || kernelId >= count) return MMBO_ERR_BAD_KERNEL_ID;
+  *bytes = 0;
+  if (dtype == MMBO_DTYPE_F32 && (kernelId == 3 || kernelId == 4) && m && n && k) *bytes = tf32_scratch(m, n, k).total;
+  return MMBO_OK;
+}
+
+int mmbo_set_workspace(void* ptr, size_t bytes) {
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
+  Workspace& w = g_ws[dev];
+  if (!w.user && w.ptr) {
+    cudaError_t e = cudaFree(w.ptr);
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (ptr && (reinterpret_cast<uintptr_t>(ptr) & 1023u)) return MMBO_ERR_WORKSPACE;
+  w.ptr = ptr;
+  w.bytes = ptr ? bytes : 0;
+  w.user = ptr != nullptr;
+  return MMBO_OK;
 }
 
 int mmbo_device_status(unsigned int* status) {

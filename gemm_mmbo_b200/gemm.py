@@ -149,3 +149,20 @@ def device_status() -> int:
     if rc > 0:
         raise MmboError(rc, "mmbo_device_status")
     return v.value
+
+
+def workspace_bytes(dtype, kernel_id: int, m: int, n: int, k: int) -> int:
+    """Scratch bytes a call with this kernel id needs (0: the kernel uses none)."""
+    out = ctypes.c_size_t()
+    rc = LIB.mmbo_gemm_workspace_bytes(_DTYPES[dtype], kernel_id, m, n, k, ctypes.byref(out))
+    if rc != 0:
+        raise MmboError(rc, "mmbo_gemm_workspace_bytes")
+    return out.value
+
+
+def set_workspace(buf, nbytes: int = 0) -> None:
+    """Lend the library a device buffer (tensor or address) as scratch for the current
+    device; `None` returns to library-managed scratch."""
+    rc = LIB.mmbo_set_workspace(_addr(buf), nbytes)
+    if rc != 0:
+        raise MmboError(rc, "mmbo_set_workspace")

@@ -52,6 +52,7 @@ extern "C" {
 #define MMBO_ERR_TENSOR_MAP (-12)       /* the driver rejected a tensor map */
 #define MMBO_ERR_DEVICE_FAULT (-13)     /* a kernel recorded a bounded-wait time-out */
 #define MMBO_ERR_TOO_LARGE (-14)
+#define MMBO_ERR_WORKSPACE (-15)        /* lent workspace too small or misaligned */
 
 /* SGEMM, fp32 storage and arithmetic.  Replaces dgemm_NT / naive_dgemm
  * (src/gemm/gemm.h:47-48, :4-5) for dtype fp32; kernelId indexes the fp32 kernel table
@@ -97,6 +98,18 @@ int mmbo_fill_f32(float* dst, size_t rows, size_t cols, size_t ld, uint64_t seed
                   int dist, float scale, size_t row0, size_t col0, size_t total_rows, void* stream);
 int mmbo_fill_f16(void* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat,
                   int dist, float scale, size_t row0, size_t col0, size_t total_rows, void* stream);
+
+/* Scratch memory.  Some kernels repack their operands into scratch memory (today: the
+ * 3xTF32 SGEMM rows of the fp32 table).  By default the library keeps one buffer per
+ * device and grows it with cudaMalloc on demand (the reference allocates nothing: its
+ * kernels need no scratch).  mmbo_gemm_workspace_bytes tells how much a call with a given
+ * kernel id needs (0 for kernels without scratch); mmbo_set_workspace lends the library a
+ * caller-owned, 1024-byte aligned device buffer for the current device (ptr = NULL hands
+ * control back to the library).  With a lent buffer the library never allocates and a
+ * call that needs more returns MMBO_ERR_WORKSPACE.  Calls that use the same scratch
+ * buffer must not overlap on the GPU. */
+int mmbo_gemm_workspace_bytes(int dtype, int kernelId, size_t m, size_t n, size_t k, size_t* bytes);
+int mmbo_set_workspace(void* ptr, size_t bytes);
 
 /* Reads and clears the device status word of the current device (synchronises the
  * device).  *status = 0 when no kernel has recorded a fault since the last call;

@@ -73,3 +73,35 @@ def test_hgemm_tensor_kernels_agree_bitwise_across_runs(cuda, mm, oracle):
         torch.cuda.synchronize()
         outs.append(dC.cpu().numpy().view(np.uint16))
     assert np.array_equal(outs[0], outs[1])
+
+
+def _pad_to8(ta, tb, m, n, k, extra=8):
+    """Pads that make every leading dimension a multiple of 8 (TMA-addressable) while
+    leaving `extra` or more padding rows below each matrix."""
+    from helpers import lead_dims
+    return tuple((-x) % 8 + extra for x in lead_dims(ta, tb, m, n, k))
+
+
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, -1])
+@pytest.mark.parametrize("ta,tb", MODES)
+def test_hgemm_ragged_extents_with_aligned_leading_dims(cuda, mm, oracle, kernel_id, ta, tb):
+    """m, n, k that are not multiples of 8 under 8-aligned leading dimensions: the tensor
+    core kernels run (TMA can address A and B) and must not touch the padding rows of C."""
+    for (m, n, k) in [(100, 60, 50), (1001, 77, 130), (37, 129, 65), (257, 255, 7), (7, 9, 3)]:
+        for beta in (0.5, 0.0):
+            case = Case(oracle, "f16", ta, tb, m, n, k, 1.0, beta, pad=_pad_to8(ta, tb, m, n, k),
+                        dist=oracle.DIST_NORMAL, scale=0.5, c_poison=(beta == 0.0))
+            run_and_check(cuda, mm, case, kernel_id)
+
+
+def test_hgemm_c_with_odd_leading_dim(cuda, mm, oracle):
+    """Only A and B need TMA-friendly layouts; C may have any leading dimension."""
+    m, n, k = 264, 136, 72
+    case = Case(oracle, "f16", False, True, m, n, k, 1.0, 0.5, pad=(0, 0, 3), dist=oracle.DIST_NORMAL, scale=0.5)
+    from helpers import to_device
+    _, dA = to_device(cuda, case.A)
+    _, dB = to_device(cuda, case.B)
+    _, dC = to_device(cuda, case.C)
+    assert mm.select_kernel("f16", False, True, m, n, k, dA, case.lda, dB, case.ldb, dC, case.ldc) != 0
+    for kid in (1, 2, 3, -1):
+        run_and_check(cuda, mm, case, kid)

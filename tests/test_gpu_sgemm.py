@@ -14,7 +14,7 @@ SHAPES = [(1, 1, 1), (5, 3, 2), (64, 64, 16), (65, 63, 17), (128, 128, 32), (129
           (200, 300, 100), (384, 256, 64), (257, 513, 129)]
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, -1])
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_sgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
     for (m, n, k) in SHAPES:
@@ -23,13 +23,13 @@ def test_sgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
             run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, -1])
 def test_sgemm_beta_zero_never_reads_c(cuda, mm, oracle, kernel_id):
     case = Case(oracle, "f32", False, True, 150, 70, 40, 2.0, 0.0, pad=(1, 2, 3), c_poison=True)
     run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, -1])
 def test_sgemm_k_zero_scales_c(cuda, mm, oracle, kernel_id):
     case = Case(oracle, "f32", False, False, 70, 33, 0, 2.0, 0.5, pad=(0, 0, 5))
     run_and_check(cuda, mm, case, kernel_id)
@@ -58,3 +58,37 @@ def test_sgemm_deterministic(cuda, mm, oracle):
         torch.cuda.synchronize()
         outs.append(dC.cpu().numpy().view(np.uint32))
     assert np.array_equal(outs[0], outs[1])
+
+
+def test_sgemm_tf32x3_accuracy_large_k(cuda, mm, oracle):
+    """The split-precision tensor-core kernels keep fp32-level accuracy over a long
+    contraction (k = 8192): relative Frobenius error <= 1e-5, like the FFMA kernels."""
+    case = Case(oracle, "f32", True, False, 384, 320, 8192, 1.0, 0.5)
+    ref = case.reference()
+    errs = {kid: run_and_check(cuda, mm, case, kid, ref=ref) for kid in (1, 3, 4)}
+    print("rel Frobenius:", errs)
+    assert max(errs.values()) <= 1e-5
+
+
+def test_sgemm_lent_workspace(cuda, mm, oracle):
+    """With a caller-owned scratch buffer the library allocates nothing: a buffer of the
+    advertised size works, a smaller one is refused before any launch."""
+    torch = cuda
+    m, n, k = 300, 200, 100
+    need = mm.workspace_bytes("f32", 3, m, n, k)
+    assert need > 0 and mm.workspace_bytes("f32", 1, m, n, k) == 0
+    case = Case(oracle, "f32", False, True, m, n, k, 1.5, -0.25, pad=(3, 3, 3))
+    buf = torch.empty(need + 1024, dtype=torch.uint8, device="cuda")
+    base = (buf.data_ptr() + 1023) // 1024 * 1024
+    try:
+        mm.set_workspace(base, need)
+        run_and_check(cuda, mm, case, 3)
+        mm.set_workspace(base, need - 1024)
+        with pytest.raises(mm.MmboError) as e:
+            run_and_check(cuda, mm, case, 3)
+        assert e.value.status == -15
+        with pytest.raises(mm.MmboError):
+            mm.set_workspace(base + 8, need)  # misaligned
+    finally:
+        mm.set_workspace(None)
+    run_and_check(cuda, mm, case, 3)  # library-managed scratch again
