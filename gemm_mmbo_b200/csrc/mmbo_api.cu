@@ -598,6 +598,8 @@ const char* mmbo_status_string(int status) {
     case MMBO_ERR_DEVICE_FAULT: return "a kernel recorded a bounded-wait time-out";
     case MMBO_ERR_TOO_LARGE: return "problem exceeds launch limits of the chosen kernel";
     case MMBO_ERR_WORKSPACE: return "the workspace lent by the caller is too small for this call";
+    case MMBO_ERR_NOALLOC_TOO_LARGE:
+      return "problem needs more scratch than the library's built-in MMBO_NOALLOC_SCRATCH_BYTES";
   }
   if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
   return "unknown status";
@@ -692,6 +694,38 @@ int mmbo_device_status(unsigned int* status) {
   }
   *status = v;
   return v ? MMBO_ERR_DEVICE_FAULT : MMBO_OK;
+}
+
+// ---------------------------------------------------------------- no-allocation SGEMM --
+// Scratch for mmbo_gemm_f32_noalloc: part of the library image, so every GPU that loads
+// the library carries these bytes until the process exits.  In host code the name below
+// is only a handle for cudaGetSymbolAddress; the device address it resolves to (one per
+// device) is what the kernels receive.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[MMBO_NOALLOC_SCRATCH_BYTES];
+static void* g_noalloc_scratch_addr[kMaxDevices];
+
+int mmbo_gemm_f32_noalloc(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
+                          const float* A, size_t lda, const float* B, size_t ldb, const float* beta, float* C,
+                          size_t ldc, void* stream) {
+  GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
+  int rc = validate(g, alpha, beta);
+  if (rc) return rc;
+  g.alpha = *alpha;
+  g.beta = *beta;
+  if (m == 0 || n == 0) return MMBO_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (k == 0) return launch_scale<float>(g, st);
+  if (tf32_scratch(m, n, k).total > (size_t)MMBO_NOALLOC_SCRATCH_BYTES) return MMBO_ERR_NOALLOC_TOO_LARGE;
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
+  if (!g_noalloc_scratch_addr[dev]) {
+    // once per device, with that device current: resolve the array's address there
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_scratch_addr[dev] = ptr;
+  }
+  return run_tf32x3<128, 3, 1>(g, g_noalloc_scratch_addr[dev], env_u32("MMBO_WGM", kF32Rows[4].wgm), st);
 }
 
 }  // extern "C"

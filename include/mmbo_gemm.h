@@ -53,6 +53,7 @@ extern "C" {
 #define MMBO_ERR_DEVICE_FAULT (-13)     /* a kernel recorded a bounded-wait time-out */
 #define MMBO_ERR_TOO_LARGE (-14)
 #define MMBO_ERR_WORKSPACE (-15)        /* lent workspace too small or misaligned */
+#define MMBO_ERR_NOALLOC_TOO_LARGE (-16) /* mmbo_gemm_f32_noalloc: scratch need exceeds the built-in array */
 
 /* SGEMM, fp32 storage and arithmetic.  Replaces dgemm_NT / naive_dgemm
  * (src/gemm/gemm.h:47-48, :4-5) for dtype fp32; kernelId indexes the fp32 kernel table
@@ -110,6 +111,37 @@ int mmbo_fill_f16(void* dst, size_t rows, size_t cols, size_t ld, uint64_t seed,
  * buffer must not overlap on the GPU. */
 int mmbo_gemm_workspace_bytes(int dtype, int kernelId, size_t m, size_t n, size_t k, size_t* bytes);
 int mmbo_set_workspace(void* ptr, size_t bytes);
+
+/* SGEMM that allocates nothing.  (No counterpart in the reference, whose kernels use no
+ * scratch memory.)
+ *
+ * Who needs it: code that must not call cudaMalloc at the moment it needs a GEMM --
+ * a real-time or latency-critical loop where an allocation (which can synchronise the
+ * whole device) is unacceptable, a plugin running inside a host application that owns
+ * all device memory and forbids its guests to allocate, or a process whose memory pool
+ * is already exhausted.  For them the split-precision tensor-core SGEMM (row 4 of the
+ * fp32 table: every operand is split into tf32 hi/lo parts and repacked before the GEMM)
+ * is offered with its scratch inside the library image instead of on the heap.
+ *
+ * Same arguments and semantics as mmbo_gemm_f32 without kernelId.  The caller still
+ * passes A, B, C.  Limits and rules:
+ *   - scratch is a fixed array of MMBO_NOALLOC_SCRATCH_BYTES bytes in the library's device
+ *     image; every GPU that loads the library holds it until the process exits;
+ *   - a call needs 8 * (m + n) * roundup(k, 32) bytes (each part rounded up to 1 KiB);
+ *     larger problems are refused with MMBO_ERR_NOALLOC_TOO_LARGE and nothing is
+ *     launched (1024 x 1024 x 1024 needs 16 MiB);
+ *   - the first call on each device looks up the array's address on that device
+ *     (cudaGetSymbolAddress, with that device current); make that first call before any
+ *     stream capture begins;
+ *   - the call performs no cudaMalloc / cudaFree and calls no allocating library routine;
+ *   - all calls on a device share the one array.  Nothing in it has to start at zero:
+ *     every element the GEMM reads is rewritten by the split pass of the same call, so
+ *     the previous call's contents are harmless.  Two calls that overlap on the GPU
+ *     (different streams) race on it: serialise them. */
+#define MMBO_NOALLOC_SCRATCH_BYTES (32u << 20)
+int mmbo_gemm_f32_noalloc(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
+                          const float* A, size_t lda, const float* B, size_t ldb, const float* beta,
+                          float* C, size_t ldc, void* stream);
 
 /* Reads and clears the device status word of the current device (synchronises the
  * device).  *status = 0 when no kernel has recorded a fault since the last call;

@@ -62,7 +62,7 @@ def test_shard_columns_rejects(mm):
 
 def test_status_strings(mm):
     assert mm.status_string(0) == "ok"
-    for code in range(-15, 0):
+    for code in range(-16, 0):
         assert mm.status_string(code) not in ("", "unknown status")
 
 
