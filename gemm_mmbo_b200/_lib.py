@@ -14,6 +14,7 @@ LIB_PATH = _PKG / "_build" / "libmmbo_gemm.so"
 _sz = ctypes.c_size_t
 _vp = ctypes.c_void_p
 _fp = ctypes.POINTER(ctypes.c_float)
+_dp = ctypes.POINTER(ctypes.c_double)
 _u32p = ctypes.POINTER(ctypes.c_uint32)
 _szp = ctypes.POINTER(ctypes.c_size_t)
 
@@ -23,6 +24,10 @@ SIGNATURES = {
                                      _fp, _vp, _sz, ctypes.c_int, _vp]),
     "mmbo_gemm_f16": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
                                      _fp, _vp, _sz, ctypes.c_int, _vp]),
+    "mmbo_gemm_f64": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _dp, _vp, _sz, _vp, _sz,
+                                     _dp, _vp, _sz, ctypes.c_int, _vp]),
+    "mmbo_fill_f64": (ctypes.c_int, [_vp, _sz, _sz, _sz, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int,
+                                     ctypes.c_float, _sz, _sz, _sz, _vp]),
     "mmbo_num_kernels": (ctypes.c_int, [ctypes.c_int]),
     "mmbo_kernel_name": (ctypes.c_char_p, [ctypes.c_int, ctypes.c_int]),
     "mmbo_kernel_params": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]),

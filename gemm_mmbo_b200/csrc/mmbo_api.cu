@@ -11,6 +11,7 @@
 #include <string.h>
 
 #include "../../include/mmbo_gemm.h"
+#include "dgemm_fma.cuh"
 #include "hgemm_tcgen05.cuh"
 #include "ref_kernels.cuh"
 #include "sgemm_ffma.cuh"
@@ -40,6 +41,12 @@ static const KernelRow kF16Rows[] = {
     {"hgemm_tcgen05_MT128x128x64_S6_CG1_WG192_WGM08", 128, 128, 192, 64, 6, 1, 8, 1},
     {"hgemm_tcgen05_MT256x256x64_S6_CG2_WG192_WGM08", 256, 256, 192, 64, 6, 2, 8, 1},
 };
+// fp64 rows (the reference's own dtype).
+static const KernelRow kF64Rows[] = {
+    {"dgemm_simple_MT032x008x01_TT01_01_WG256", 32, 8, 256, 1, 1, 1, 1, 0},
+    {"dgemm_fma_MT064x064x16_TT04_04_WG256_WGM08", 64, 64, 256, 16, 2, 1, 8, 0},
+};
+constexpr int kNumF64 = sizeof(kF64Rows) / sizeof(KernelRow);
 constexpr int kNumF32 = sizeof(kF32Rows) / sizeof(KernelRow);
 constexpr int kNumF16 = sizeof(kF16Rows) / sizeof(KernelRow);
 
@@ -51,6 +58,10 @@ static const KernelRow* rows_of(int dtype, int* count) {
   if (dtype == MMBO_DTYPE_F16) {
     *count = kNumF16;
     return kF16Rows;
+  }
+  if (dtype == MMBO_DTYPE_F64) {
+    *count = kNumF64;
+    return kF64Rows;
   }
   *count = 0;
   return nullptr;
@@ -493,6 +504,34 @@ static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
   return MMBO_ERR_BAD_KERNEL_ID;
 }
 
+static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStream_t st) {
+  if (g.m == 0 || g.n == 0) return MMBO_OK;
+  const double* A = static_cast<const double*>(g.A);
+  const double* B = static_cast<const double*>(g.B);
+  double* C = static_cast<double*>(g.C);
+  if (g.k == 0 || id == 0) {
+    const size_t gx = (g.m + 31) / 32, gy = (g.n + 7) / 8;
+    if (gy > 65535 || gx > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
+    dim3 grid((unsigned)gx, (unsigned)gy), block(32, 8);
+    if (g.k == 0) scale_c_f64_kernel<<<grid, block, 0, st>>>(g.m, g.n, beta, C, g.ldc);
+    else gemm_simple_f64_kernel<<<grid, block, 0, st>>>(g.transA, g.transB, g.m, g.n, g.k, alpha, A, g.lda, B, g.ldb, beta, C, g.ldc);
+    return (int)cudaGetLastError();
+  }
+  if (id != 1) return MMBO_ERR_BAD_KERNEL_ID;
+  DgemmParams p;
+  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
+  p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
+  p.alpha = alpha; p.beta = beta; p.wgm = env_u32("MMBO_WGM", kF64Rows[1].wgm);
+  const size_t gx = (g.m + kDgBM - 1) / kDgBM, gy = (g.n + kDgBN - 1) / kDgBN;
+  if (gy > 65535) return MMBO_ERR_TOO_LARGE;
+  dim3 grid((unsigned)gx, (unsigned)gy);
+  if (!g.transA && !g.transB) dgemm_fma_kernel<false, false><<<grid, kDgThreads, 0, st>>>(A, B, C, p);
+  else if (!g.transA && g.transB) dgemm_fma_kernel<false, true><<<grid, kDgThreads, 0, st>>>(A, B, C, p);
+  else if (g.transA && !g.transB) dgemm_fma_kernel<true, false><<<grid, kDgThreads, 0, st>>>(A, B, C, p);
+  else dgemm_fma_kernel<true, true><<<grid, kDgThreads, 0, st>>>(A, B, C, p);
+  return (int)cudaGetLastError();
+}
+
 static int run_f16(const GemmArgs& g, int id, cudaStream_t st) {
   if (g.m == 0 || g.n == 0) return MMBO_OK;
   if (g.k == 0) return launch_scale<__half>(g, st);
@@ -544,6 +583,17 @@ int mmbo_gemm_f16(int transA, int transB, size_t m, size_t n, size_t k, const fl
   return run_f16(g, id, static_cast<cudaStream_t>(stream));
 }
 
+int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const double* alpha, const double* A,
+                  size_t lda, const double* B, size_t ldb, const double* beta, double* C, size_t ldc,
+                  int kernelId, void* stream) {
+  GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
+  int rc = validate(g, reinterpret_cast<const float*>(alpha), reinterpret_cast<const float*>(beta));
+  if (rc) return rc;
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF64)) return MMBO_ERR_BAD_KERNEL_ID;
+  const int id = kernelId == MMBO_KERNEL_AUTO ? 1 : kernelId;
+  return run_f64(g, *alpha, *beta, id, static_cast<cudaStream_t>(stream));
+}
+
 int mmbo_num_kernels(int dtype) {
   int n = 0;
   rows_of(dtype, &n);
@@ -577,6 +627,7 @@ int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, si
   if (rc) return rc;
   if (dtype == MMBO_DTYPE_F32) return select_f32(g);
   if (dtype == MMBO_DTYPE_F16) return select_f16(g);
+  if (dtype == MMBO_DTYPE_F64) return g.k == 0 ? 0 : 1;
   return MMBO_ERR_BAD_DTYPE;
 }
 
@@ -639,6 +690,9 @@ static int fill_common(int dtype, void* dst, size_t rows, size_t cols, size_t ld
   if (dtype == MMBO_DTYPE_F32)
     fill_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(static_cast<float*>(dst), rows, cols, ld, seed, mat,
                                                          dist, scale, row0, col0, total_rows);
+  else if (dtype == MMBO_DTYPE_F64)
+    fill_kernel<double><<<(unsigned)blocks, 256, 0, st>>>(static_cast<double*>(dst), rows, cols, ld, seed, mat,
+                                                          dist, scale, row0, col0, total_rows);
   else
     fill_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<__half*>(dst), rows, cols, ld, seed,
                                                           mat, dist, scale, row0, col0, total_rows);
@@ -648,6 +702,11 @@ static int fill_common(int dtype, void* dst, size_t rows, size_t cols, size_t ld
 int mmbo_fill_f32(float* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat, int dist,
                   float scale, size_t row0, size_t col0, size_t total_rows, void* stream) {
   return fill_common(MMBO_DTYPE_F32, dst, rows, cols, ld, seed, mat, dist, scale, row0, col0, total_rows, stream);
+}
+
+int mmbo_fill_f64(double* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat, int dist,
+                  float scale, size_t row0, size_t col0, size_t total_rows, void* stream) {
+  return fill_common(MMBO_DTYPE_F64, dst, rows, cols, ld, seed, mat, dist, scale, row0, col0, total_rows, stream);
 }
 
 int mmbo_fill_f16(void* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat, int dist,

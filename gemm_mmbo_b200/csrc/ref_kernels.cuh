@@ -23,6 +23,8 @@ template <>
 __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ double from_f32<double>(float v) { return (double)v; }
 
 // One thread per C element, 32 x 8 thread blocks (32 consecutive rows per warp so that
 // C and non-transposed A accesses coalesce).  fp32 accumulation in increasing l.
@@ -44,6 +46,31 @@ __global__ void gemm_simple_kernel(int transA, int transB, size_t m, size_t n, s
   float r = alpha * acc;
   if (beta != 0.0f) r = fmaf(beta, to_f32<T>(C[i + j * ldc]), r);
   C[i + j * ldc] = from_f32<T>(r);
+}
+
+// binary64 variant of the kernel above (accumulation and scalars in binary64).
+__global__ void gemm_simple_f64_kernel(int transA, int transB, size_t m, size_t n, size_t k, double alpha,
+                                       const double* __restrict__ A, size_t lda, const double* __restrict__ B,
+                                       size_t ldb, double beta, double* __restrict__ C, size_t ldc) {
+  const size_t i = (size_t)blockIdx.x * 32 + threadIdx.x;
+  const size_t j = (size_t)blockIdx.y * 8 + threadIdx.y;
+  if (i >= m || j >= n) return;
+  double acc = 0.0;
+  for (size_t l = 0; l < k; ++l) {
+    const double a = transA ? A[l + i * lda] : A[i + l * lda];
+    const double b = transB ? B[j + l * ldb] : B[l + j * ldb];
+    acc = fma(a, b, acc);
+  }
+  double r = alpha * acc;
+  if (beta != 0.0) r = fma(beta, C[i + j * ldc], r);
+  C[i + j * ldc] = r;
+}
+
+__global__ void scale_c_f64_kernel(size_t m, size_t n, double beta, double* __restrict__ C, size_t ldc) {
+  const size_t i = (size_t)blockIdx.x * 32 + threadIdx.x;
+  const size_t j = (size_t)blockIdx.y * 8 + threadIdx.y;
+  if (i >= m || j >= n) return;
+  C[i + j * ldc] = beta != 0.0 ? beta * C[i + j * ldc] : 0.0;
 }
 
 // k == 0: C = beta*C (or zero when beta == 0).

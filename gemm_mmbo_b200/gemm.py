@@ -13,12 +13,13 @@ import ctypes
 
 from ._lib import LIB
 
-DTYPE_F32, DTYPE_F16 = 0, 1
+DTYPE_F32, DTYPE_F16, DTYPE_F64 = 0, 1, 2
 KERNEL_AUTO = -1
 DIST_UNIFORM, DIST_NORMAL, DIST_ZERO = 0, 1, 2
 MAT_A, MAT_B, MAT_C = 0, 1, 2
 
-_DTYPES = {"f32": DTYPE_F32, "f16": DTYPE_F16, DTYPE_F32: DTYPE_F32, DTYPE_F16: DTYPE_F16}
+_DTYPES = {"f32": DTYPE_F32, "f16": DTYPE_F16, "f64": DTYPE_F64, DTYPE_F32: DTYPE_F32, DTYPE_F16: DTYPE_F16,
+           DTYPE_F64: DTYPE_F64}
 
 
 class MmboError(RuntimeError):
@@ -59,18 +60,19 @@ def gemm(dtype, transA: bool, transB: bool, m: int, n: int, k: int, alpha: float
     """C = alpha*op(A)*op(B) + beta*C on the current device, asynchronously on `stream`
     (default: torch's current stream)."""
     dt = _DTYPES[dtype]
-    fn = LIB.mmbo_gemm_f32 if dt == DTYPE_F32 else LIB.mmbo_gemm_f16
-    a, b = ctypes.c_float(alpha), ctypes.c_float(beta)
-    rc = fn(int(bool(transA)), int(bool(transB)), m, n, k, ctypes.byref(a), _addr(A), lda, _addr(B), ldb,
-            ctypes.byref(b), _addr(C), ldc, kernelId, _stream(stream))
+    name = {DTYPE_F32: "mmbo_gemm_f32", DTYPE_F16: "mmbo_gemm_f16", DTYPE_F64: "mmbo_gemm_f64"}[dt]
+    scalar = ctypes.c_double if dt == DTYPE_F64 else ctypes.c_float
+    a, b = scalar(alpha), scalar(beta)
+    rc = getattr(LIB, name)(int(bool(transA)), int(bool(transB)), m, n, k, ctypes.byref(a), _addr(A), lda,
+                            _addr(B), ldb, ctypes.byref(b), _addr(C), ldc, kernelId, _stream(stream))
     if rc != 0:
-        raise MmboError(rc, "mmbo_gemm_f32" if dt == DTYPE_F32 else "mmbo_gemm_f16")
+        raise MmboError(rc, name)
 
 
 def _wrap(dtype, ta, tb):
     def f(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId=KERNEL_AUTO, stream=None):
         gemm(dtype, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId, stream)
-    f.__doc__ = (f"{'s' if dtype == 'f32' else 'h'}gemm_{'T' if ta else 'N'}{'T' if tb else 'N'}: "
+    f.__doc__ = (f"{dict(f32='s', f16='h', f64='d')[dtype]}gemm_{'T' if ta else 'N'}{'T' if tb else 'N'}: "
                  "argument order of the reference's dgemm_NT (src/gemm/gemm.h:47-48).")
     return f
 
@@ -79,6 +81,8 @@ sgemm_NN, sgemm_NT = _wrap("f32", False, False), _wrap("f32", False, True)
 sgemm_TN, sgemm_TT = _wrap("f32", True, False), _wrap("f32", True, True)
 hgemm_NN, hgemm_NT = _wrap("f16", False, False), _wrap("f16", False, True)
 hgemm_TN, hgemm_TT = _wrap("f16", True, False), _wrap("f16", True, True)
+dgemm_NN, dgemm_NT = _wrap("f64", False, False), _wrap("f64", False, True)
+dgemm_TN, dgemm_TT = _wrap("f64", True, False), _wrap("f64", True, True)
 
 
 def num_kernels(dtype) -> int:
@@ -135,7 +139,7 @@ def fill(dtype, dst, rows: int, cols: int, ld: int, *, seed: int = 1234, mat: in
          stream=None) -> None:
     """Seeded operand generation on the device (include/mmbo_rng.h)."""
     dt = _DTYPES[dtype]
-    fn = LIB.mmbo_fill_f32 if dt == DTYPE_F32 else LIB.mmbo_fill_f16
+    fn = {DTYPE_F32: LIB.mmbo_fill_f32, DTYPE_F16: LIB.mmbo_fill_f16, DTYPE_F64: LIB.mmbo_fill_f64}[dt]
     rc = fn(_addr(dst), rows, cols, ld, seed, mat, dist, float(scale), row0, col0,
             rows if total_rows is None else total_rows, _stream(stream))
     if rc != 0:

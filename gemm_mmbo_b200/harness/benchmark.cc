@@ -10,7 +10,7 @@
 //           over its Tensile table, benchmark.cc:89-109)
 //   type 2  the vendor library (cuBLAS here, rocBLAS in the reference, benchmark.cc:110-117)
 //
-//   options: --dtype f16|f32 (default f16)   --trans NN|NT|TN|TT (default NT)
+//   options: --dtype f16|f32|f64 (default f16; f64 is the reference's own type)   --trans NN|NT|TN|TT (default NT)
 //            --alpha a --beta b (defaults -1, 1: the reference's HPL update, benchmark.cc:21)
 //            --kernel id (type 0 only)  --seed s  --iters n (timed launches, default 20)
 //
@@ -54,7 +54,7 @@ bool parse(int argc, char** argv, Options* o) {
   for (int i = 8; i + 1 < argc; i += 2) {
     const std::string key = argv[i];
     const char* v = argv[i + 1];
-    if (key == "--dtype") o->dtype = strcmp(v, "f32") == 0 ? MMBO_DTYPE_F32 : MMBO_DTYPE_F16;
+    if (key == "--dtype") o->dtype = strcmp(v, "f32") == 0 ? MMBO_DTYPE_F32 : strcmp(v, "f64") == 0 ? MMBO_DTYPE_F64 : MMBO_DTYPE_F16;
     else if (key == "--trans" && strlen(v) == 2) { o->transA = v[0] == 'T'; o->transB = v[1] == 'T'; }
     else if (key == "--alpha") o->alpha = (float)atof(v);
     else if (key == "--beta") o->beta = (float)atof(v);
@@ -71,10 +71,11 @@ bool parse(int argc, char** argv, Options* o) {
 double peak_tflops(int dtype) {
   if (dtype == MMBO_DTYPE_F16) return 2250.0;
   int dev = 0, sms = 148, khz = 1965000;
+  const double lanes = dtype == MMBO_DTYPE_F64 ? 64.0 : 128.0;  // FMA lanes per SM per clock
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
-  return sms * 128.0 * 2.0 * khz * 1e3 / 1e12;
+  return sms * lanes * 2.0 * khz * 1e3 / 1e12;
 }
 
 }  // namespace
@@ -86,7 +87,7 @@ int main(int argc, char** argv) {
                 "[--alpha a] [--beta b] [--kernel id] [--seed s] [--iters n]\n");
     return 2;
   }
-  const size_t esz = o.dtype == MMBO_DTYPE_F32 ? 4 : 2;
+  const size_t esz = o.dtype == MMBO_DTYPE_F32 ? 4 : o.dtype == MMBO_DTYPE_F64 ? 8 : 2;
   const size_t rowsA = o.transA ? o.K : o.M, colsA = o.transA ? o.M : o.K;
   const size_t rowsB = o.transB ? o.N : o.K, colsB = o.transB ? o.K : o.N;
   void *dA = nullptr, *dB = nullptr, *dC = nullptr;
@@ -96,6 +97,8 @@ int main(int argc, char** argv) {
   auto fill = [&](void* p, size_t rows, size_t cols, size_t ld, unsigned mat) {
     if (ld < rows) return (int)MMBO_ERR_BAD_LDC;
     cudaMemset(p, 0, ld * cols * esz);
+    if (o.dtype == MMBO_DTYPE_F64)
+      return mmbo_fill_f64((double*)p, rows, cols, ld, o.seed, mat, MMBO_DIST_UNIFORM_PM1, 1.f, 0, 0, rows, nullptr);
     return o.dtype == MMBO_DTYPE_F32
                ? mmbo_fill_f32((float*)p, rows, cols, ld, o.seed, mat, MMBO_DIST_UNIFORM_PM1, 1.f, 0, 0, rows, nullptr)
                : mmbo_fill_f16(p, rows, cols, ld, o.seed, mat, MMBO_DIST_UNIFORM_PM1, 1.f, 0, 0, rows, nullptr);
@@ -105,7 +108,16 @@ int main(int argc, char** argv) {
   MMBO_CHECK(fill(dC, o.M, o.N, o.ldc, MMBO_MAT_C));
 
   const char trans[3] = {o.transA ? 'T' : 'N', o.transB ? 'T' : 'N', 0};
-  const char* prefix = o.dtype == MMBO_DTYPE_F32 ? "s" : "h";
+  const char* prefix = o.dtype == MMBO_DTYPE_F32 ? "s" : o.dtype == MMBO_DTYPE_F64 ? "d" : "h";
+  double alpha64 = o.alpha, beta64 = o.beta;
+  // one call of the library for the chosen dtype (binary64 takes double scalars, like the reference)
+  auto gemm_call = [&](int id) -> int {
+    if (o.dtype == MMBO_DTYPE_F64)
+      return ::dgemm(o.transA, o.transB, o.M, o.N, o.K, &alpha64, (const double*)dA, o.lda, (const double*)dB,
+                         o.ldb, &beta64, (double*)dC, o.ldc, id);
+    return mmbo::launchGemm(o.dtype, o.transA, o.transB, o.M, o.N, o.K, &o.alpha, dA, o.lda, dB, o.ldb, &o.beta, dC,
+                            o.ldc, id);
+  };
   const double flops = 2.0 * (double)o.M * (double)o.N * (double)o.K;
   const double peak = peak_tflops(o.dtype);
   cudaEvent_t ev0, ev1;
@@ -113,14 +125,11 @@ int main(int argc, char** argv) {
 
   auto time_kernel = [&](int id, double* tflops) -> int {
     for (int w = 0; w < 3; ++w) {
-      int rc = mmbo::launchGemm(o.dtype, o.transA, o.transB, o.M, o.N, o.K, &o.alpha, dA, o.lda, dB, o.ldb,
-                                &o.beta, dC, o.ldc, id);
+      int rc = gemm_call(id);
       if (rc) return rc;
     }
     MMBO_GPU_TIMER_START(seconds, ev0, ev1, nullptr);
-    for (int it = 0; it < o.iters; ++it)
-      mmbo::launchGemm(o.dtype, o.transA, o.transB, o.M, o.N, o.K, &o.alpha, dA, o.lda, dB, o.ldb, &o.beta, dC,
-                       o.ldc, id);
+    for (int it = 0; it < o.iters; ++it) gemm_call(id);
     MMBO_GPU_TIMER_END(seconds, ev0, ev1, nullptr);
     seconds /= o.iters;
     *tflops = 1e-12 * flops / seconds;
@@ -156,8 +165,12 @@ int main(int argc, char** argv) {
   } else {
     cublasHandle_t h;
     if (cublasCreate(&h) != CUBLAS_STATUS_SUCCESS) { std::fprintf(stderr, "cublasCreate failed\n"); return 1; }
-    const cudaDataType_t dt = o.dtype == MMBO_DTYPE_F32 ? CUDA_R_32F : CUDA_R_16F;
+    const cudaDataType_t dt = o.dtype == MMBO_DTYPE_F32 ? CUDA_R_32F : o.dtype == MMBO_DTYPE_F64 ? CUDA_R_64F : CUDA_R_16F;
     auto call = [&]() {
+      if (o.dtype == MMBO_DTYPE_F64)
+        return cublasDgemm(h, o.transA ? CUBLAS_OP_T : CUBLAS_OP_N, o.transB ? CUBLAS_OP_T : CUBLAS_OP_N, (int)o.M,
+                           (int)o.N, (int)o.K, &alpha64, (const double*)dA, (int)o.lda, (const double*)dB, (int)o.ldb,
+                           &beta64, (double*)dC, (int)o.ldc);
       return cublasGemmEx(h, o.transA ? CUBLAS_OP_T : CUBLAS_OP_N, o.transB ? CUBLAS_OP_T : CUBLAS_OP_N, (int)o.M,
                           (int)o.N, (int)o.K, &o.alpha, dA, dt, (int)o.lda, dB, dt, (int)o.ldb, &o.beta, dC, dt,
                           (int)o.ldc, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);

@@ -33,6 +33,7 @@ extern "C" {
 
 #define MMBO_DTYPE_F32 0
 #define MMBO_DTYPE_F16 1
+#define MMBO_DTYPE_F64 2
 
 #define MMBO_KERNEL_AUTO (-1)
 
@@ -69,6 +70,13 @@ int mmbo_gemm_f16(int transA, int transB, size_t m, size_t n, size_t k, const fl
                   const void* A, size_t lda, const void* B, size_t ldb, const float* beta,
                   void* C, size_t ldc, int kernelId, void* stream);
 
+/* DGEMM, binary64 storage and arithmetic: the reference's own data type.  Literal
+ * replacement for dgemm_NT (transA = 0, transB = 1) and naive_dgemm
+ * (src/gemm/gemm.h:47-48, :4-5), which take double* alpha/beta. */
+int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const double* alpha,
+                  const double* A, size_t lda, const double* B, size_t ldb, const double* beta,
+                  double* C, size_t ldc, int kernelId, void* stream);
+
 /* Kernel table -- the counterpart of naive_kernels / kernels / *_kernel_parameters in
  * src/gemm/constants.h:4-135.  out[8] = {MT0 (tile along m), MT1 (tile along n), threads,
  * DepthU (k per stage), stages, ctaGroup, wgm, usesTensorCores}. */
@@ -98,6 +106,8 @@ int mmbo_shard_columns(size_t n, int nGpus, int rank, size_t align, size_t* col0
 int mmbo_fill_f32(float* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat,
                   int dist, float scale, size_t row0, size_t col0, size_t total_rows, void* stream);
 int mmbo_fill_f16(void* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat,
+                  int dist, float scale, size_t row0, size_t col0, size_t total_rows, void* stream);
+int mmbo_fill_f64(double* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat,
                   int dist, float scale, size_t row0, size_t col0, size_t total_rows, void* stream);
 
 /* Scratch memory.  Some kernels repack their operands into scratch memory (today: the

@@ -84,6 +84,24 @@ MMBO_DEFINE_GEMM(gemm_TN, 1, 0)
 MMBO_DEFINE_GEMM(gemm_TT, 1, 1)
 #undef MMBO_DEFINE_GEMM
 
+// The reference's own entry points, name for name and argument for argument
+// (src/gemm/gemm.h:47-48 and :4-5): binary64, NT layout, void return.  A failure is
+// reported on stderr; the process keeps running.
+inline void dgemm_NT(size_t m, size_t n, size_t k, double* alpha, const double* A, size_t lda, const double* B,
+                     size_t ldb, double* beta, double* C, size_t ldc, int kernelId) {
+  const int rc = mmbo_gemm_f64(0, 1, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId, nullptr);
+  if (rc != 0) std::fprintf(stderr, "dgemm_NT: status %d: %s\n", rc, mmbo_status_string(rc));
+}
+inline void naive_dgemm(size_t m, size_t n, size_t k, double* alpha, const double* A, size_t lda, const double* B,
+                        size_t ldb, double* beta, double* C, size_t ldc, int kernelId) {
+  dgemm_NT(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId);
+}
+inline int dgemm(int transA, int transB, size_t m, size_t n, size_t k, double* alpha, const double* A, size_t lda,
+                 const double* B, size_t ldb, double* beta, double* C, size_t ldc,
+                 int kernelId = MMBO_KERNEL_AUTO, cudaStream_t stream = nullptr) {
+  return mmbo_gemm_f64(transA, transB, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId, stream);
+}
+
 // Event-pair timer on a stream; elapsed time in seconds, like the reference's macros.
 #define MMBO_GPU_TIMER_START(elapsed, ev_start, ev_stop, stream) \
   do {                                                           \

@@ -60,7 +60,10 @@ def lib() -> ctypes.CDLL:
                                           _vp, _sz, _sz, _vp, _vp, _vp]
         L.oracle_rel_frobenius.restype = ctypes.c_double
         L.oracle_rel_frobenius.argtypes = [ctypes.c_int, _sz, _sz, _vp, _sz, _vp, _sz]
-        for name in ("oracle_fill_f32", "oracle_fill_f16"):
+        L.oracle_gemm_f64.restype = None
+        L.oracle_gemm_f64.argtypes = [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, ctypes.c_double, _vp, _sz,
+                                      _vp, _sz, ctypes.c_double, _vp, _sz, _vp, _sz]
+        for name in ("oracle_fill_f32", "oracle_fill_f16", "oracle_fill_f64"):
             f = getattr(L, name)
             f.restype = None
             f.argtypes = [_vp, _sz, _sz, _sz, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int,
@@ -88,7 +91,7 @@ def _ptr(a: np.ndarray | None):
 
 
 def _storage(dtype: str):
-    return {"f32": np.float32, "f16": np.float16}[dtype]
+    return {"f32": np.float32, "f16": np.float16, "f64": np.float64}[dtype]
 
 
 def fill(dtype: str, rows: int, cols: int, ld: int | None = None, *, seed: int = 1234,
@@ -99,7 +102,7 @@ def fill(dtype: str, rows: int, cols: int, ld: int | None = None, *, seed: int =
     ld = rows if ld is None else ld
     assert ld >= rows
     out = np.full((cols, ld), pad, dtype=_storage(dtype))
-    fn = lib().oracle_fill_f32 if dtype == "f32" else lib().oracle_fill_f16
+    fn = getattr(lib(), f"oracle_fill_{dtype}")
     fn(_ptr(out), rows, cols, ld, seed, mat, dist, float(scale), row0, col0,
        rows if total_rows is None else total_rows)
     return out
@@ -110,6 +113,8 @@ def gemm(dtype: str, transA: bool, transB: bool, m: int, n: int, k: int, alpha: 
          C: np.ndarray | None, ldc: int, naive: bool = False) -> np.ndarray:
     """Unrounded binary64 result, shape (n, m) (column-major m x n, ld = m)."""
     out = np.empty((n, m), dtype=np.float64)
+    if dtype == "f64":  # long-double accumulation; there is no separate naive variant
+        naive = False
     name = f"oracle_gemm_{'naive_' if naive else ''}{dtype}"
     getattr(lib(), name)(int(transA), int(transB), m, n, k, float(alpha), _ptr(A), lda,
                          _ptr(B), ldb, float(beta), _ptr(C), ldc, _ptr(out), max(m, 1))
@@ -130,7 +135,7 @@ def gemm_sampled(dtype: str, transA: bool, transB: bool, k: int, alpha: float, A
 def rel_frobenius(dtype: str, m: int, n: int, got: np.ndarray, ldg: int,
                   ref: np.ndarray) -> float:
     """||got - ref||_F / ||ref||_F over the m x n window; got is (n, ldg) storage-typed."""
-    return float(lib().oracle_rel_frobenius(0 if dtype == "f32" else 1, m, n, _ptr(got), ldg,
+    return float(lib().oracle_rel_frobenius({"f32": 0, "f16": 1, "f64": 2}[dtype], m, n, _ptr(got), ldg,
                                             _ptr(ref), max(m, 1)))
 
 

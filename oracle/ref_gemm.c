@@ -40,9 +40,11 @@
 
 #define DT_F32 0
 #define DT_F16 1
+#define DT_F64 2
 
 static inline double load_elem(const void *p, size_t idx, int dt) {
   if (dt == DT_F32) return (double)((const float *)p)[idx];
+  if (dt == DT_F64) return ((const double *)p)[idx];
   return (double)mmbo_f16_bits_to_f32(((const uint16_t *)p)[idx]);
 }
 
@@ -168,6 +170,37 @@ void oracle_gemm_naive_f16(int transA, int transB, size_t m, size_t n, size_t k,
                            double *Cout, size_t ldo) {
   gemm_naive(DT_F16, transA, transB, m, n, k, (double)alpha, A, lda, B, ldb,
              (double)beta, Cin, ldc, Cout, ldo);
+}
+
+/* binary64 storage (the reference's own dtype: src/gemm/gemm.h:4,47 take double).  A
+ * binary64 accumulator would be no more accurate than the kernel under test, so this
+ * one accumulates in long double (64-bit significand on x86-64) in increasing l. */
+void oracle_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, double alpha,
+                     const double *A, size_t lda, const double *B, size_t ldb, double beta,
+                     const double *Cin, size_t ldc, double *Cout, size_t ldo) {
+#pragma omp parallel for schedule(dynamic, 1)
+  for (ptrdiff_t j = 0; j < (ptrdiff_t)n; ++j)
+    for (size_t i = 0; i < m; ++i) {
+      long double acc = 0.0L;
+      for (size_t l = 0; l < k; ++l) {
+        long double a = transA ? A[l + i * lda] : A[i + l * lda];
+        long double b = transB ? B[(size_t)j + l * ldb] : B[l + (size_t)j * ldb];
+        acc += a * b;
+      }
+      long double r = (long double)alpha * acc;
+      if (beta != 0.0) r += (long double)beta * (long double)Cin[i + (size_t)j * ldc];
+      Cout[i + (size_t)j * ldo] = (double)r;
+    }
+}
+
+void oracle_fill_f64(double *dst, size_t rows, size_t cols, size_t ld, uint64_t seed,
+                     uint32_t mat, int dist, float scale, size_t row0, size_t col0,
+                     size_t total_rows) {
+#pragma omp parallel for schedule(static)
+  for (ptrdiff_t j = 0; j < (ptrdiff_t)cols; ++j)
+    for (size_t i = 0; i < rows; ++i)
+      dst[i + (size_t)j * ld] =
+          (double)mmbo_rng_value(seed, mat, row0 + i, col0 + (size_t)j, total_rows, dist, scale);
 }
 
 /* Selected elements only: out[t] = element (rows[t], cols[t]) of the result.  Used to

@@ -7,7 +7,7 @@ import numpy as np
 
 GUARD = 256  # elements of sentinel before and after every device buffer
 
-TOL = {"f32": 1e-5, "f16": 2e-3}  # relative Frobenius error (BASELINE north_star)
+TOL = {"f32": 1e-5, "f16": 2e-3, "f64": 1e-13}  # relative Frobenius error (fp32/fp16: BASELINE north_star)
 
 
 def lead_dims(ta, tb, m, n, k):
@@ -50,7 +50,7 @@ def to_device(torch, host: np.ndarray):
 
 
 def bits(a: np.ndarray) -> np.ndarray:
-    return a.view(np.uint16 if a.dtype == np.float16 else np.uint32)
+    return a.view({2: np.uint16, 4: np.uint32, 8: np.uint64}[a.dtype.itemsize])
 
 
 def run_and_check(torch, mm, case: Case, kernel_id=-1, tol=None, ref=None):

@@ -1,0 +1,35 @@
+"""DGEMM (binary64, the reference's own data type) against the oracle's long-double
+accumulation: relative Frobenius error <= 1e-13, all transpose modes, ragged shapes,
+padded leading dimensions, the reference's HPL update (alpha = -1, beta = 1, NT)."""
+import pytest
+
+from helpers import Case, run_and_check
+
+pytestmark = pytest.mark.gpu
+
+MODES = [(False, False), (False, True), (True, False), (True, True)]
+SHAPES = [(1, 1, 1), (5, 3, 2), (64, 64, 16), (65, 63, 17), (129, 127, 33), (200, 300, 100), (257, 130, 129)]
+
+
+@pytest.mark.parametrize("kernel_id", [0, 1, -1])
+@pytest.mark.parametrize("ta,tb", MODES)
+def test_dgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
+    for (m, n, k) in SHAPES:
+        for pad in ((0, 0, 0), (3, 1, 2)):
+            case = Case(oracle, "f64", ta, tb, m, n, k, -1.0, 1.0, pad=pad, seed=m + 31 * n)
+            run_and_check(cuda, mm, case, kernel_id)
+
+
+@pytest.mark.parametrize("kernel_id", [0, 1])
+def test_dgemm_beta_zero_and_k_zero(cuda, mm, oracle, kernel_id):
+    run_and_check(cuda, mm, Case(oracle, "f64", False, True, 150, 70, 40, 2.0, 0.0, pad=(1, 2, 3), c_poison=True),
+                  kernel_id)
+    run_and_check(cuda, mm, Case(oracle, "f64", False, True, 70, 33, 0, 2.0, 0.5, pad=(0, 0, 5)), kernel_id)
+
+
+def test_dgemm_reference_sweep_shape(cuda, mm, oracle):
+    """One point of the reference's run.sh sweep (M multiple of 384, N = 2048, K = 384, ldc = 44160,
+    alpha = -1, beta = 1, NT) through the reference-named Python mirror."""
+    m, n, k = 1536, 2048, 384
+    case = Case(oracle, "f64", False, True, m, n, k, -1.0, 1.0, pad=(0, 0, 44160 - m))
+    run_and_check(cuda, mm, case, -1)
