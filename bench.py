@@ -305,12 +305,9 @@ def main():
         e2e_steps = max(3, min(args.steps, 10 if P == 1 else 3))
 
         def e2e_step():
-            A.copy_(hA, non_blocking=True)
-            B.copy_(hB, non_blocking=True)
-            if use_c:
-                C.copy_(hC, non_blocking=True)
-            mm.gemm("f16", ta, tb, m, ncols, k, w["alpha"], A, ra, B, rb, w["beta"], C, m, args.kernel)
-            hC.copy_(C, non_blocking=True)
+            # one library call on host operands: A staged once, B/C column panels copied in,
+            # multiplied and copied out on overlapping streams; returns when hC is complete
+            mm.gemm_host("f16", ta, tb, m, ncols, k, w["alpha"], hA, ra, hB, rb, w["beta"], hC, m, args.kernel)
 
         for _ in range(2):
             e2e_step()
@@ -329,7 +326,7 @@ def main():
         h2d = (hA.numel() + hB.numel() + (hC.numel() if use_c else 0)) * 2
         e2e = {"value": flops / (ems / e2e_steps * 1e-3) / 1e12, "unit": UNIT,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": hC.numel() * 2, "steps": e2e_steps,
-               "ms_per_step": ems / e2e_steps}
+               "ms_per_step": ems / e2e_steps, "api": "mmbo_gemm_f16_host (pinned host A, B, C)"}
 
     cpu = None
     if rank == 0 and P == 1 and not args.no_cpu_baseline:

@@ -28,6 +28,10 @@ SIGNATURES = {
                                      _dp, _vp, _sz, ctypes.c_int, _vp]),
     "mmbo_fill_f64": (ctypes.c_int, [_vp, _sz, _sz, _sz, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int,
                                      ctypes.c_float, _sz, _sz, _sz, _vp]),
+    "mmbo_gemm_f32_host": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
+                                          _fp, _vp, _sz, ctypes.c_int]),
+    "mmbo_gemm_f16_host": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
+                                          _fp, _vp, _sz, ctypes.c_int]),
     "mmbo_num_kernels": (ctypes.c_int, [ctypes.c_int]),
     "mmbo_kernel_name": (ctypes.c_char_p, [ctypes.c_int, ctypes.c_int]),
     "mmbo_kernel_params": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]),

@@ -14,9 +14,10 @@
 //   * No operand is ever transposed in memory: NN/NT/TN/TT only change which tensor
 //     map describes an operand and whether its shared-memory tile is "K-major"
 //     (contraction index contiguous: transA = T, transB = N) or "MN-major".
-//   * Roles (192 threads): warp 0 = TMA producer (one elected lane), warp 1 = tensor
-//     memory owner + UMMA issuer (one lane), warps 2-5 = epilogue, one per 32-lane
-//     quarter of tensor memory.
+//   * Roles: warp 0 = TMA producer (one elected lane), warp 1 = tensor memory owner +
+//     UMMA issuer (one lane), then EW epilogue warps: one per 32-lane quarter of tensor
+//     memory (192 threads), or two per quarter that split the columns (320 threads) for
+//     shapes with a short contraction, where the epilogue is what bounds the kernel.
 //   * STAGES-deep ring of 128-byte-swizzled shared-memory tiles fed by TMA; two
 //     accumulators in tensor memory so the epilogue of tile i overlaps the main loop
 //     of tile i+1 (the idea sketched by the reference's two-tiles-per-work-group kernel,
@@ -45,24 +46,25 @@ namespace mmbo {
 constexpr int kTileN = 128;  // problem-N extent of a CTA tile = UMMA M
 constexpr int kBlockK = 64;  // fp16 elements per stage along K = one 128-byte swizzle row
 constexpr int kUmmaK = 16;   // K extent of one kind::f16 UMMA
-constexpr int kEpiWarps = 4;
 constexpr int kEpiBufBytes = 32 * 128;  // 32 C columns x 64 rows of fp16, per warp buffer
-constexpr int kHgemmThreads = 192;
 
 // CG = CTAs cooperating on one UMMA (cta_group): 1, or 2 for a CTA pair that shares a
 // 256-lane accumulator; each CTA of a pair stages its own 128 rows of op(B) and its own
 // half (TM / 2 rows) of op(A).
-template <int TM, int STAGES, int CG = 1>
+// EW = epilogue warps: 4 (one per 32-lane quarter of tensor memory) or 8 (two per
+// quarter, each taking half of the accumulator's columns).
+template <int TM, int STAGES, int CG = 1, int EW = 4>
 struct HgemmSmem {
+  static constexpr int kThreads = 64 + 32 * EW;
   static constexpr int kAopRows = TM / CG;                // rows of op(A) staged by one CTA
   static constexpr int kBopBytes = kTileN * kBlockK * 2;  // op(B) tile  (UMMA A operand)
   static constexpr int kAopBytes = kAopRows * kBlockK * 2;  // op(A) tile  (UMMA B operand)
   static constexpr int kStageBytes = kBopBytes + kAopBytes;
   static constexpr int kEpiOffset = STAGES * kStageBytes;
-  static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiBufBytes;
+  static constexpr int kEpiBytes = EW * 2 * kEpiBufBytes;
   static constexpr int kBarOffset = kEpiOffset + kEpiBytes;
-  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], cload[4][2]
-  static constexpr int kNumBars = 2 * STAGES + 4 + 2 * kEpiWarps;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], cload[EW][2]
+  static constexpr int kNumBars = 2 * STAGES + 4 + 2 * EW;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
   static constexpr int kTotal = kMiscOffset + 16;
   static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024 bytes
@@ -75,6 +77,9 @@ struct HgemmParams {
   float alpha, beta;
   __half* c;       // C and its leading dimension, for the epilogue without TMA
   uint32_t ldc;
+  uint32_t diag;   // diagnostic builds, results wrong by design (the reference keeps such
+                   // kernels too: test_main_loop.s has no C store, error_kernel_000.s no waits):
+                   // bit 0 = no C store, bit 1 = no tensor-memory drain either
   uint32_t c_tma;  // 1: C goes through the tensor map (16-byte aligned base, ldc % 8 == 0,
                    // m % 8 == 0: TMA stores whole 16-byte units, so a ragged m would spill
                    // into the padding rows below the matrix)
@@ -90,13 +95,17 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-template <int TM, int STAGES, bool A_KMAJOR, bool B_KMAJOR, int CG = 1>
-__global__ void __launch_bounds__(kHgemmThreads, 1)
+template <int TM, int STAGES, bool A_KMAJOR, bool B_KMAJOR, int CG = 1, int EW = 4>
+__global__ void __launch_bounds__(64 + 32 * EW, 1)
 hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_c, const HgemmParams p) {
-  using L = HgemmSmem<TM, STAGES, CG>;
+  using L = HgemmSmem<TM, STAGES, CG, EW>;
   static_assert(TM == 128 || TM == 256, "TM is the UMMA N extent");
+  static_assert(EW == 4 || EW == 8, "one or two epilogue warps per tensor-memory quarter");
+  // 64-row chunks of the accumulator each epilogue warp drains per tile
+  constexpr uint32_t kChunksPerWarp = (TM / 64) / (EW / 4);
+  static_assert(kChunksPerWarp >= 1, "tile too narrow for this many epilogue warps");
   static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair per UMMA");
   constexpr uint32_t kTmemCols = 2 * TM;
   // CTA pair: rank 0 (the leader) issues every UMMA and owns the barriers that count
@@ -132,9 +141,9 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (uint32_t a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), kEpiWarps * CG);
+      mbar_init(tmem_empty_bar(a), EW * CG);
     }
-    for (uint32_t w = 0; w < kEpiWarps; ++w)
+    for (uint32_t w = 0; w < EW; ++w)
       for (uint32_t b = 0; b < 2; ++b) mbar_init(cload_bar(w, b), 1);
     fence_mbar_init();
     prefetch_tensormap(&tmap_a);
@@ -270,49 +279,95 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     __syncwarp();
   } else {
-    // ===== epilogue: warp owns tensor-memory lanes [32q, 32q+32) = 32 columns of C =====
+    // ===== epilogue: warp owns tensor-memory lanes [32q, 32q+32) = 32 columns of C, and
+    // kChunksPerWarp 64-row chunks of them (all of them with 4 warps, half with 8) =====
     const uint32_t q = warp & 3u;
     const uint32_t epi_w = warp - 2u;
+    const uint32_t col_base = (epi_w >> 2) * kChunksPerWarp * 64u;  // first accumulator column of this warp
     const uint32_t buf_base = smem_base + L::kEpiOffset + epi_w * 2u * kEpiBufBytes;
     uint8_t* buf_gen = smem_gen + L::kEpiOffset + epi_w * 2u * kEpiBufBytes;
     const bool use_c = (p.beta != 0.0f);
     const bool c_tma = p.c_tma != 0u;
     const float alpha = p.alpha, beta = p.beta;
-    uint32_t local_tile = 0, chunk_ctr = 0;
+    uint32_t local_tile = 0;
     uint32_t cphase[2] = {0u, 0u};
     bool ok = true;
     for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers, ++local_tile) {
       uint32_t tm_idx, tn_idx;
       mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
-      const uint32_t m0 = tm_idx * TM;
+      const uint32_t m0 = tm_idx * TM + col_base;
       const uint32_t ncol0 = (tn_idx * CG + cta_rank) * kTileN + 32u * q;  // first C column of this warp
       const uint32_t acc = local_tile & 1u;
       const uint32_t acc_phase = (local_tile >> 1) & 1u;
+      // Staging tile b (two per warp): row t = C column ncol0 + t, 64 fp16 = C rows of one
+      // chunk; the 16-byte piece j of a row lives at piece j ^ (t & 7) (128-byte TMA swizzle).
+      // With beta != 0 the old C of the first two chunks is requested now, before the wait
+      // for the accumulator, so that its latency overlaps the main loop of this tile.
+      if (c_tma && use_c) {
+        if (lane == 0) tma_store_wait_read<0>();  // both buffers' stores have read them
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (uint32_t c = 0; c < (kChunksPerWarp < 2u ? kChunksPerWarp : 2u); ++c) {
+            const uint32_t mrow0 = m0 + 64u * c;
+            if (mrow0 < p.m && ncol0 < p.n) {
+              mbar_expect_tx(cload_bar(epi_w, c), kEpiBufBytes);
+              tma_load_2d(buf_base + c * kEpiBufBytes, &tmap_c, cload_bar(epi_w, c),
+                          static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
+            }
+          }
+        }
+      }
       // Every lane polls; the verdict is made warp-uniform so that the aligned
       // tcgen05 instructions below always run with a converged warp.
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag,
                                              kFaultWaitTmemFull, acc));
       if (!ok) break;
       tcgen05_fence_after();
-      const uint32_t t_warp = tmem_base + ((32u * q) << 16) + acc * TM;
-#pragma unroll 1
-      for (uint32_t c = 0; c < TM / 64; ++c, ++chunk_ctr) {
-        const uint32_t b = chunk_ctr & 1u;
+      const uint32_t t_warp = tmem_base + ((32u * q) << 16) + acc * TM + col_base;
+      const bool drain = (p.diag & 2u) == 0u;
+      auto release_accumulator = [&]() {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CG == 2) mbar_arrive_cluster(mapa_shared(tmem_empty_bar(acc), 0u));
+          else mbar_arrive(tmem_empty_bar(acc));
+        }
+      };
+      // With at most 128 accumulator columns per warp the whole share is pulled into
+      // registers first and the accumulator handed back at once: for short contractions
+      // the time an accumulator stays occupied bounds the kernel.
+      constexpr bool kEarlyDrain = kChunksPerWarp <= 2;
+      uint32_t racc[kEarlyDrain ? 2 * kChunksPerWarp : 2][32];
+      if constexpr (kEarlyDrain) {
+#pragma unroll
+        for (uint32_t i = 0; i < 2 * kChunksPerWarp; ++i) {
+          if (drain) tmem_ld_32x32(t_warp + 32u * i, racc[i]);
+          else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) racc[i][e] = 0u;
+          }
+        }
+        tmem_ld_wait();
+        release_accumulator();
+      }
+      auto do_chunk = [&](const uint32_t c) {
+        const uint32_t b = c & 1u;
         const uint32_t sbuf = buf_base + b * kEpiBufBytes;
         uint8_t* gbuf = buf_gen + b * kEpiBufBytes;
         const uint32_t mrow0 = m0 + 64u * c;
         const bool in_range = (mrow0 < p.m) && (ncol0 < p.n);  // warp-uniform
         const bool load_c = use_c && in_range;
-        // Staging tile: row t = C column ncol0 + t, 64 fp16 = rows mrow0 .. mrow0+63; the
-        // 16-byte piece j of a row lives at piece j ^ (t & 7) (the 128-byte TMA swizzle).
         if (c_tma) {
-          // The store issued from this buffer two chunks ago must have read it.
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-          if (load_c && lane == 0) {
-            mbar_expect_tx(cload_bar(epi_w, b), kEpiBufBytes);
-            tma_load_2d(sbuf, &tmap_c, cload_bar(epi_w, b), static_cast<int32_t>(mrow0),
-                        static_cast<int32_t>(ncol0));
+          if (!use_c || c >= 2u) {
+            // The store issued from this buffer two chunks ago must have read it.
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+            if (load_c && lane == 0) {  // chunks beyond the two requested up front
+              mbar_expect_tx(cload_bar(epi_w, b), kEpiBufBytes);
+              tma_load_2d(sbuf, &tmap_c, cload_bar(epi_w, b), static_cast<int32_t>(mrow0),
+                          static_cast<int32_t>(ncol0));
+            }
           }
         } else {
           __syncwarp();  // the previous plain write-out of this buffer is complete
@@ -333,27 +388,29 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             __syncwarp();
           }
         }
-        uint32_t r[32];
-        tmem_ld_32x32(t_warp + 64u * c, r);
+        if constexpr (!kEarlyDrain) {
+          if (drain) {
+            tmem_ld_32x32(t_warp + 64u * c, racc[0]);
+            tmem_ld_32x32(t_warp + 64u * c + 32u, racc[1]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) racc[0][e] = racc[1][e] = 0u;
+          }
+        }
         if (c_tma && load_c) {
           if (!mbar_wait(cload_bar(epi_w, b), cphase[b], abort_flag, kFaultWaitCLoad, epi_w)) ok = false;
           cphase[b] ^= 1u;
         }
         // `ok` may differ between lanes only after a time-out, when the data is
         // discarded anyway; keep the warp converged for the aligned tcgen05 ops.
+        if constexpr (!kEarlyDrain) {
+          tmem_ld_wait();
+          // This warp's part of the accumulator is read: hand it back to the UMMA issuer.
+          if (c == kChunksPerWarp - 1) release_accumulator();
+        }
 #pragma unroll
         for (uint32_t h = 0; h < 2; ++h) {
-          if (h == 1) tmem_ld_32x32(t_warp + 64u * c + 32u, r);
-          tmem_ld_wait();
-          if (h == 1 && c == TM / 64 - 1) {
-            // Accumulator fully read: hand it back to the UMMA issuer.
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-              if constexpr (CG == 2) mbar_arrive_cluster(mapa_shared(tmem_empty_bar(acc), 0u));
-              else mbar_arrive(tmem_empty_bar(acc));
-            }
-          }
+          const uint32_t(&r)[32] = racc[kEarlyDrain ? 2 * c + h : h];
 #pragma unroll
           for (uint32_t jj = 0; jj < 4; ++jj) {
             const uint32_t j = 4u * h + jj;  // 16-byte chunk of the 128-byte row
@@ -382,13 +439,13 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (in_range && ok)
+            if (in_range && ok && (p.diag & 1u) == 0u)
               tma_store_2d(&tmap_c, sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
             tma_store_commit();
           }
         } else {
           __syncwarp();
-          if (in_range) {
+          if (in_range && (p.diag & 1u) == 0u) {
             const __half* hb = reinterpret_cast<const __half*>(gbuf);
 #pragma unroll 2
             for (uint32_t t = 0; t < 32; ++t) {
@@ -403,6 +460,13 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         ok = __all_sync(0xffffffffu, ok);
+      };
+      if constexpr (kEarlyDrain) {  // unrolled: the register copy of the accumulator is indexed statically
+#pragma unroll
+        for (uint32_t c = 0; c < kChunksPerWarp; ++c) do_chunk(c);
+      } else {
+#pragma unroll 1
+        for (uint32_t c = 0; c < kChunksPerWarp; ++c) do_chunk(c);
       }
     }
     if (lane == 0) tma_store_wait_all<0>();

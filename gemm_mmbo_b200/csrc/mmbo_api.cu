@@ -40,6 +40,7 @@ static const KernelRow kF16Rows[] = {
     {"hgemm_tcgen05_MT256x128x64_S4_CG1_WG192_WGM08", 256, 128, 192, 64, 4, 1, 8, 1},
     {"hgemm_tcgen05_MT128x128x64_S6_CG1_WG192_WGM08", 128, 128, 192, 64, 6, 1, 8, 1},
     {"hgemm_tcgen05_MT256x256x64_S6_CG2_WG192_WGM08", 256, 256, 192, 64, 6, 2, 8, 1},
+    {"hgemm_tcgen05_MT256x256x64_S5_CG2_WG320_WGM08", 256, 256, 320, 64, 5, 2, 8, 1},
 };
 // fp64 rows (the reference's own dtype).
 static const KernelRow kF64Rows[] = {
@@ -222,11 +223,11 @@ static bool hgemm_tma_ok(const GemmArgs& g) {
   return aligned16(g.A) && aligned16(g.B) && g.lda % 8 == 0 && g.ldb % 8 == 0 && g.k > 0;
 }
 
-template <int TM, int STAGES, int CG, bool AK, bool BK_>
+template <int TM, int STAGES, int CG, int EW, bool AK, bool BK_>
 static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                              const HgemmParams& p, uint64_t tiles, cudaStream_t st) {
-  using L = HgemmSmem<TM, STAGES, CG>;
-  auto kern = hgemm_tcgen05_kernel<TM, STAGES, AK, BK_, CG>;
+  using L = HgemmSmem<TM, STAGES, CG, EW>;
+  auto kern = hgemm_tcgen05_kernel<TM, STAGES, AK, BK_, CG, EW>;
   static bool attr_done[kMaxDevices] = {};
   static int max_walkers[kMaxDevices] = {};
   const int dev = current_device();
@@ -240,7 +241,7 @@ static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const
       // SMs leave one SM unpaired).
       cudaLaunchConfig_t q = {};
       q.gridDim = dim3((unsigned)(2 * walkers));
-      q.blockDim = dim3(kHgemmThreads);
+      q.blockDim = dim3(L::kThreads);
       q.dynamicSmemBytes = L::kDynamic;
       cudaLaunchAttribute qa[1];
       qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -256,7 +257,7 @@ static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const
   const unsigned walkers = (unsigned)(tiles < (uint64_t)max_walkers[dev] ? tiles : (uint64_t)max_walkers[dev]);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(walkers * CG);
-  cfg.blockDim = dim3(kHgemmThreads);
+  cfg.blockDim = dim3(L::kThreads);
   cfg.dynamicSmemBytes = L::kDynamic;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -266,7 +267,7 @@ static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const
   return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
 }
 
-template <int TM, int STAGES, int CG>
+template <int TM, int STAGES, int CG, int EW = 4>
 static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
   CUtensorMap ta, tb, tc;
   int rc;
@@ -298,12 +299,13 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   p.wgm = wgm;
   p.alpha = g.alpha; p.beta = g.beta;
   p.c = static_cast<__half*>(g.C); p.ldc = (uint32_t)g.ldc; p.c_tma = c_tma ? 1u : 0u;
+  p.diag = env_u32("MMBO_DIAG", 0);  // diagnostic builds (no C store / no drain): never set in production
   const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
   if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-  if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, true, true>(ta, tb, tc, p, tiles, st);
-  if (g.transA && g.transB) return launch_hgemm_inst<TM, STAGES, CG, true, false>(ta, tb, tc, p, tiles, st);
-  if (!g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, false, true>(ta, tb, tc, p, tiles, st);
-  return launch_hgemm_inst<TM, STAGES, CG, false, false>(ta, tb, tc, p, tiles, st);
+  if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, true>(ta, tb, tc, p, tiles, st);
+  if (g.transA && g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, false>(ta, tb, tc, p, tiles, st);
+  if (!g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, false, true>(ta, tb, tc, p, tiles, st);
+  return launch_hgemm_inst<TM, STAGES, CG, EW, false, false>(ta, tb, tc, p, tiles, st);
 }
 
 // ------------------------------------------------------------------ scratch memory --
@@ -481,7 +483,9 @@ static int select_f16(const GemmArgs& g) {
   const double s1 = 0.80 * eff(t1, sms) * fill(t1, 256, 128);
   const double s2 = 0.70 * eff(t2, sms) * fill(t2, 128, 128);
   const double s3 = 1.00 * eff(t3, sms / 2) * fill(t3, 256, 256);
-  if (s3 >= s1 && s3 >= s2) return 3;
+  // Short contractions are bound by how fast accumulators are drained: the variant with
+  // eight epilogue warps wins there and ties on long ones.
+  if (s3 >= s1 && s3 >= s2) return g.k <= 1536 ? 4 : 3;
   return s1 >= s2 ? 1 : 2;
 }
 
@@ -546,8 +550,127 @@ static int run_f16(const GemmArgs& g, int id, cudaStream_t st) {
     case 3:
       if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
       return launch_hgemm_tcgen05<256, 6, 2>(g, env_u32("MMBO_WGM", kF16Rows[3].wgm), st);
+    case 4:
+      if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
+      return launch_hgemm_tcgen05<256, 5, 2, 8>(g, env_u32("MMBO_WGM", kF16Rows[4].wgm), st);
   }
   return MMBO_ERR_BAD_KERNEL_ID;
+}
+
+// ------------------------------------------------------------------ host operands ----
+// GEMM on operands that live in HOST memory (what the reference's harness does by hand
+// around its kernel: hipMalloc + hipMemcpy in, launch, hipMemcpy out --
+// src/gemm/benchmark.cc:57-63, src/gemm/test.cc:53-66,89).  A is copied once; B and C
+// travel in column panels through two device buffers each, so that the copy-in of panel
+// j+1, the GEMM of panel j and the copy-out of panel j-1 overlap on three streams.
+struct HostPipe {
+  bool ready;
+  cudaStream_t s_in, s_mm, s_out;
+  cudaEvent_t ev_a, ev_in[2], ev_mm[2], ev_out[2];
+  void* buf;
+  size_t bytes;
+};
+static HostPipe g_pipe[kMaxDevices];
+
+static int pipe_setup(HostPipe& hp, size_t bytes) {
+  cudaError_t e;
+  if (!hp.ready) {
+    if ((e = cudaStreamCreateWithFlags(&hp.s_in, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
+    if ((e = cudaStreamCreateWithFlags(&hp.s_mm, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
+    if ((e = cudaStreamCreateWithFlags(&hp.s_out, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
+    cudaEventCreateWithFlags(&hp.ev_a, cudaEventDisableTiming);
+    for (int i = 0; i < 2; ++i) {
+      cudaEventCreateWithFlags(&hp.ev_in[i], cudaEventDisableTiming);
+      cudaEventCreateWithFlags(&hp.ev_mm[i], cudaEventDisableTiming);
+      cudaEventCreateWithFlags(&hp.ev_out[i], cudaEventDisableTiming);
+    }
+    hp.ready = true;
+  }
+  if (hp.bytes < bytes) {
+    if (hp.buf) cudaFree(hp.buf);
+    hp.buf = nullptr;
+    hp.bytes = 0;
+    if ((e = cudaMalloc(&hp.buf, bytes)) != cudaSuccess) return (int)e;
+    hp.bytes = bytes;
+  }
+  return MMBO_OK;
+}
+
+static int gemm_host(int dtype, const GemmArgs& h, int kernelId) {
+  const size_t es = dtype == MMBO_DTYPE_F32 ? 4 : 2;
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
+  if (h.m == 0 || h.n == 0) return MMBO_OK;
+  // Device layouts are compact (leading dimension = extent rounded up to 16 bytes'
+  // worth of elements, so that TMA can address them).
+  const size_t al = 16 / es;
+  const size_t rowsA = h.transA ? h.k : h.m, colsA = h.transA ? h.m : h.k;
+  const size_t dlda = align_up(rowsA ? rowsA : 1, al), dldc = align_up(h.m, al);
+  // panel width: about an eighth of n, a multiple of 256 columns
+  size_t np = align_up((h.n + 7) / 8, 256);
+  if (np > h.n) np = h.n;
+  const size_t panels = (h.n + np - 1) / np;
+  const size_t dldb = h.transB ? align_up(np, al) : align_up(h.k ? h.k : 1, al);
+  const size_t colsBp = h.transB ? h.k : np;  // columns of a device B panel
+  const size_t a_bytes = align_up(dlda * colsA * es, 1024);
+  const size_t b_bytes = align_up(dldb * (colsBp ? colsBp : 1) * es, 1024);
+  const size_t c_bytes = align_up(dldc * np * es, 1024);
+  HostPipe& hp = g_pipe[dev];
+  int rc = pipe_setup(hp, a_bytes + 2 * b_bytes + 2 * c_bytes);
+  if (rc) return rc;
+  char* dA = static_cast<char*>(hp.buf);
+  char* dB[2] = {dA + a_bytes, dA + a_bytes + b_bytes};
+  char* dC[2] = {dA + a_bytes + 2 * b_bytes, dA + a_bytes + 2 * b_bytes + c_bytes};
+  const bool use_c = h.beta != 0.f;
+  cudaError_t e;
+  if (h.k > 0) {
+    e = cudaMemcpy2DAsync(dA, dlda * es, h.A, h.lda * es, rowsA * es, colsA, cudaMemcpyHostToDevice, hp.s_in);
+    if (e != cudaSuccess) return (int)e;
+  }
+  cudaEventRecord(hp.ev_a, hp.s_in);
+  cudaStreamWaitEvent(hp.s_mm, hp.ev_a, 0);
+  for (size_t j = 0; j < panels; ++j) {
+    const int b = (int)(j & 1);
+    const size_t j0 = j * np, w = (j0 + np <= h.n) ? np : h.n - j0;
+    if (j >= 2) {
+      cudaStreamWaitEvent(hp.s_in, hp.ev_mm[b], 0);   // B buffer: its GEMM has run
+      cudaStreamWaitEvent(hp.s_in, hp.ev_out[b], 0);  // C buffer: its result has left
+    }
+    if (h.k > 0) {
+      const char* src = static_cast<const char*>(h.B) + (h.transB ? j0 : j0 * h.ldb) * es;
+      if (h.transB) e = cudaMemcpy2DAsync(dB[b], dldb * es, src, h.ldb * es, w * es, h.k, cudaMemcpyHostToDevice, hp.s_in);
+      else e = cudaMemcpy2DAsync(dB[b], dldb * es, src, h.ldb * es, h.k * es, w, cudaMemcpyHostToDevice, hp.s_in);
+      if (e != cudaSuccess) return (int)e;
+    }
+    char* hCj = static_cast<char*>(h.C) + j0 * h.ldc * es;
+    if (use_c) {
+      e = cudaMemcpy2DAsync(dC[b], dldc * es, hCj, h.ldc * es, h.m * es, w, cudaMemcpyHostToDevice, hp.s_in);
+      if (e != cudaSuccess) return (int)e;
+    }
+    cudaEventRecord(hp.ev_in[b], hp.s_in);
+    cudaStreamWaitEvent(hp.s_mm, hp.ev_in[b], 0);
+    if (j >= 2 && !use_c) cudaStreamWaitEvent(hp.s_mm, hp.ev_out[b], 0);
+    GemmArgs g = h;
+    g.n = w; g.A = dA; g.lda = dlda; g.B = dB[b]; g.ldb = dldb; g.C = dC[b]; g.ldc = dldc;
+    int id = kernelId;
+    if (dtype == MMBO_DTYPE_F32) {
+      if (id == MMBO_KERNEL_AUTO) id = select_f32(g);
+      rc = run_f32(g, id, hp.s_mm);
+    } else {
+      if (id == MMBO_KERNEL_AUTO) id = select_f16(g);
+      rc = run_f16(g, id, hp.s_mm);
+    }
+    if (rc) { cudaDeviceSynchronize(); return rc; }
+    cudaEventRecord(hp.ev_mm[b], hp.s_mm);
+    cudaStreamWaitEvent(hp.s_out, hp.ev_mm[b], 0);
+    e = cudaMemcpy2DAsync(hCj, h.ldc * es, dC[b], dldc * es, h.m * es, w, cudaMemcpyDeviceToHost, hp.s_out);
+    if (e != cudaSuccess) return (int)e;
+    cudaEventRecord(hp.ev_out[b], hp.s_out);
+  }
+  // the caller's buffers hold the result when this returns
+  if ((e = cudaStreamSynchronize(hp.s_out)) != cudaSuccess) return (int)e;
+  if ((e = cudaStreamSynchronize(hp.s_mm)) != cudaSuccess) return (int)e;
+  return (int)cudaStreamSynchronize(hp.s_in);
 }
 
 }  // namespace mmbo
@@ -581,6 +704,30 @@ int mmbo_gemm_f16(int transA, int transB, size_t m, size_t n, size_t k, const fl
   if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF16)) return MMBO_ERR_BAD_KERNEL_ID;
   const int id = kernelId == MMBO_KERNEL_AUTO ? select_f16(g) : kernelId;
   return run_f16(g, id, static_cast<cudaStream_t>(stream));
+}
+
+int mmbo_gemm_f32_host(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha, const float* A,
+                       size_t lda, const float* B, size_t ldb, const float* beta, float* C, size_t ldc,
+                       int kernelId) {
+  GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
+  int rc = validate(g, alpha, beta);
+  if (rc) return rc;
+  g.alpha = *alpha;
+  g.beta = *beta;
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF32)) return MMBO_ERR_BAD_KERNEL_ID;
+  return gemm_host(MMBO_DTYPE_F32, g, kernelId);
+}
+
+int mmbo_gemm_f16_host(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha, const void* A,
+                       size_t lda, const void* B, size_t ldb, const float* beta, void* C, size_t ldc,
+                       int kernelId) {
+  GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
+  int rc = validate(g, alpha, beta);
+  if (rc) return rc;
+  g.alpha = *alpha;
+  g.beta = *beta;
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF16)) return MMBO_ERR_BAD_KERNEL_ID;
+  return gemm_host(MMBO_DTYPE_F16, g, kernelId);
 }
 
 int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const double* alpha, const double* A,

@@ -109,12 +109,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned int fault_code, unsigned int detail,
                                           uint64_t limit_ns = MMBO_WAIT_LIMIT_NS) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // Fast path: poll without touching the global timer (reading it costs far more than
+  // a poll, and almost every wait ends within a few polls).
+#pragma unroll 1
+  for (uint32_t i = 0; i < 1024u; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
+    if ((++spins & 255u) == 0u) {
       if (*abort_flag) return false;
       if (global_timer_ns() - t0 > limit_ns) {
         report_fault(fault_code, detail);

@@ -69,6 +69,27 @@ def gemm(dtype, transA: bool, transB: bool, m: int, n: int, k: int, alpha: float
         raise MmboError(rc, name)
 
 
+def gemm_host(dtype, transA: bool, transB: bool, m: int, n: int, k: int, alpha: float, A, lda: int, B,
+              ldb: int, beta: float, C, ldc: int, kernelId: int = KERNEL_AUTO) -> None:
+    """Same GEMM with A, B, C in host memory (pinned torch tensors, numpy arrays or raw
+    addresses); returns when C holds the result."""
+    dt = _DTYPES[dtype]
+    name = {DTYPE_F32: "mmbo_gemm_f32_host", DTYPE_F16: "mmbo_gemm_f16_host"}[dt]
+    a, b = ctypes.c_float(alpha), ctypes.c_float(beta)
+    rc = getattr(LIB, name)(int(bool(transA)), int(bool(transB)), m, n, k, ctypes.byref(a), _haddr(A), lda,
+                            _haddr(B), ldb, ctypes.byref(b), _haddr(C), ldc, kernelId)
+    if rc != 0:
+        raise MmboError(rc, name)
+
+
+def _haddr(x):
+    if x is None or isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return int(x.data_ptr())
+    return int(x.ctypes.data)  # numpy
+
+
 def _wrap(dtype, ta, tb):
     def f(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId=KERNEL_AUTO, stream=None):
         gemm(dtype, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId, stream)

@@ -70,6 +70,20 @@ int mmbo_gemm_f16(int transA, int transB, size_t m, size_t n, size_t k, const fl
                   const void* A, size_t lda, const void* B, size_t ldb, const float* beta,
                   void* C, size_t ldc, int kernelId, void* stream);
 
+/* The same GEMMs on operands in HOST memory: A, B, C are host pointers (pinned memory
+ * gives full copy bandwidth), everything else as above.  This is the whole round trip
+ * the reference's harness performs around its kernel (device allocation, hipMemcpy in,
+ * launch, hipMemcpy out: src/gemm/benchmark.cc:57-63, src/gemm/test.cc:53-66,89), done
+ * inside the library with the copies of B/C column panels overlapped with the GEMM on
+ * internal streams.  The call returns when C holds the result.  The library keeps the
+ * device staging buffers (A plus two B and two C panels) between calls. */
+int mmbo_gemm_f32_host(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
+                       const float* A, size_t lda, const float* B, size_t ldb, const float* beta,
+                       float* C, size_t ldc, int kernelId);
+int mmbo_gemm_f16_host(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
+                       const void* A, size_t lda, const void* B, size_t ldb, const float* beta,
+                       void* C, size_t ldc, int kernelId);
+
 /* DGEMM, binary64 storage and arithmetic: the reference's own data type.  Literal
  * replacement for dgemm_NT (transA = 0, transB = 1) and naive_dgemm
  * (src/gemm/gemm.h:47-48, :4-5), which take double* alpha/beta. */

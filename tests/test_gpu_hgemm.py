@@ -15,7 +15,7 @@ SHAPES = [(8, 8, 8), (64, 32, 16), (128, 128, 64), (256, 128, 128), (136, 72, 20
           (520, 392, 328), (1024, 512, 640), (40, 1000, 96), (1000, 40, 96)]
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, 3, -1, 0])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, -1, 0])
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_hgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
     for (m, n, k) in SHAPES:
@@ -25,13 +25,13 @@ def test_hgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
             run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, 3, -1, 0])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, -1, 0])
 def test_hgemm_beta_zero_never_reads_c(cuda, mm, oracle, kernel_id):
     case = Case(oracle, "f16", False, True, 264, 200, 72, 2.0, 0.0, pad=(0, 8, 16), c_poison=True)
     run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, 3, -1])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, -1])
 def test_hgemm_many_tiles_per_cta(cuda, mm, oracle, kernel_id):
     """More tiles than SMs: every persistent CTA walks several tiles, so stage and
     accumulator phases wrap many times."""
@@ -82,7 +82,7 @@ def _pad_to8(ta, tb, m, n, k, extra=8):
     return tuple((-x) % 8 + extra for x in lead_dims(ta, tb, m, n, k))
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, 3, -1])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, -1])
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_hgemm_ragged_extents_with_aligned_leading_dims(cuda, mm, oracle, kernel_id, ta, tb):
     """m, n, k that are not multiples of 8 under 8-aligned leading dimensions: the tensor
@@ -103,5 +103,5 @@ def test_hgemm_c_with_odd_leading_dim(cuda, mm, oracle):
     _, dB = to_device(cuda, case.B)
     _, dC = to_device(cuda, case.C)
     assert mm.select_kernel("f16", False, True, m, n, k, dA, case.lda, dB, case.ldb, dC, case.ldc) != 0
-    for kid in (1, 2, 3, -1):
+    for kid in (1, 2, 3, 4, -1):
         run_and_check(cuda, mm, case, kid)
