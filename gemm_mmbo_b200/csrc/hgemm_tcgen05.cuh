@@ -77,6 +77,7 @@ struct HgemmParams {
   float alpha, beta;
   __half* c;       // C and its leading dimension, for the epilogue without TMA
   uint32_t ldc;
+  unsigned long long* trace;  // optional event trace (clock stamps of CTA 0), null in production
   uint32_t diag;   // diagnostic builds, results wrong by design (the reference keeps such
                    // kernels too: test_main_loop.s has no C store, error_kernel_000.s no waits):
                    // bit 0 = no C store, bit 1 = no tensor-memory drain either
@@ -93,6 +94,14 @@ __device__ __forceinline__ uint32_t cluster_cta_rank() {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Event trace for performance work: when HgemmParams::trace is set, the UMMA issuer and
+// the first epilogue warp of CTA 0 record clock stamps per tile (16 slots per tile:
+// 0-7 epilogue, 8-15 issuer).  The counterpart of the reference's #ifdef DEBUG prints
+// (src/gemm/driver.h:38-55), for the device side.
+__device__ __forceinline__ void trace_stamp(unsigned long long* trace, uint32_t tile_slot, uint32_t ev) {
+  if (trace != nullptr && blockIdx.x == 0 && tile_slot < 64u) trace[tile_slot * 16u + ev] = clock64();
 }
 
 template <int TM, int STAGES, bool A_KMAJOR, bool B_KMAJOR, int CG = 1, int EW = 4>
@@ -242,10 +251,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers, ++local_tile) {
         const uint32_t acc = local_tile & 1u;
         const uint32_t acc_phase = (local_tile >> 1) & 1u;
+        trace_stamp(p.trace, local_tile, 8);
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, kFaultWaitTmemEmpty, acc)) {
           ok = false;
           break;
         }
+        trace_stamp(p.trace, local_tile, 9);
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TM;
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
@@ -271,6 +282,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             phase ^= 1u;
           }
         }
+        trace_stamp(p.trace, local_tile, 10);
         if (ok) {  // accumulator complete (in both CTAs of a pair)
           if constexpr (CG == 2) umma_commit_pair(tmem_full_bar(acc), 3);
           else umma_commit(tmem_full_bar(acc));
@@ -303,6 +315,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // chunk; the 16-byte piece j of a row lives at piece j ^ (t & 7) (128-byte TMA swizzle).
       // With beta != 0 the old C of the first two chunks is requested now, before the wait
       // for the accumulator, so that its latency overlaps the main loop of this tile.
+      const bool tracer = (warp == 2u && lane == 0u);
+      if (tracer) trace_stamp(p.trace, local_tile, 0);
       if (c_tma && use_c) {
         if (lane == 0) tma_store_wait_read<0>();  // both buffers' stores have read them
         __syncwarp();
@@ -318,11 +332,24 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+      if (tracer) trace_stamp(p.trace, local_tile, 1);
+      // ... and the old C of the tile after this one is pulled into L2 now, one whole tile
+      // ahead, so that those requests will not have to go to HBM.
+      if (c_tma && use_c && lane == 0 && tile + num_walkers < num_tiles) {
+        uint32_t nm, nn;
+        mmbo_tile_from_serial(tile + num_walkers, p.tiles_m, p.tiles_n, p.wgm, &nm, &nn);
+        const uint32_t nm0 = nm * TM + col_base, nn0 = (nn * CG + cta_rank) * kTileN + 32u * q;
+#pragma unroll
+        for (uint32_t c = 0; c < kChunksPerWarp; ++c)
+          if (nm0 + 64u * c < p.m && nn0 < p.n)
+            tma_prefetch_l2_2d(&tmap_c, static_cast<int32_t>(nm0 + 64u * c), static_cast<int32_t>(nn0));
+      }
       // Every lane polls; the verdict is made warp-uniform so that the aligned
       // tcgen05 instructions below always run with a converged warp.
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag,
                                              kFaultWaitTmemFull, acc));
       if (!ok) break;
+      if (tracer) trace_stamp(p.trace, local_tile, 2);
       tcgen05_fence_after();
       const uint32_t t_warp = tmem_base + ((32u * q) << 16) + acc * TM + col_base;
       const bool drain = (p.diag & 2u) == 0u;
@@ -350,6 +377,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         tmem_ld_wait();
         release_accumulator();
+        if (tracer) trace_stamp(p.trace, local_tile, 3);
       }
       auto do_chunk = [&](const uint32_t c) {
         const uint32_t b = c & 1u;
@@ -459,6 +487,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
         }
+        if (tracer) trace_stamp(p.trace, local_tile, 5 + (c == 0 ? 0 : 1));
         ok = __all_sync(0xffffffffu, ok);
       };
       if constexpr (kEarlyDrain) {  // unrolled: the register copy of the accumulator is indexed statically

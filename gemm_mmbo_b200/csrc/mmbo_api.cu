@@ -165,6 +165,10 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem_byt
   return r == CUDA_SUCCESS ? MMBO_OK : MMBO_ERR_TENSOR_MAP;
 }
 
+// Device buffer for the optional event trace of the tcgen05 kernels (see trace_stamp).
+static unsigned long long* g_trace_buffer = nullptr;
+constexpr size_t kTraceWords = 64 * 16;
+
 // ------------------------------------------------------------------ launches ---------
 template <typename T>
 static int launch_simple(const GemmArgs& g, cudaStream_t st) {
@@ -299,6 +303,7 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   p.wgm = wgm;
   p.alpha = g.alpha; p.beta = g.beta;
   p.c = static_cast<__half*>(g.C); p.ldc = (uint32_t)g.ldc; p.c_tma = c_tma ? 1u : 0u;
+  p.trace = g_trace_buffer;  // null unless mmbo_debug_trace armed it
   p.diag = env_u32("MMBO_DIAG", 0);  // diagnostic builds (no C store / no drain): never set in production
   const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
   if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
@@ -884,6 +889,24 @@ int mmbo_set_workspace(void* ptr, size_t bytes) {
   w.bytes = ptr ? bytes : 0;
   w.user = ptr != nullptr;
   return MMBO_OK;
+}
+
+int mmbo_debug_trace(int enable, unsigned long long* out, size_t words) {
+  // enable != 0: allocate and clear the trace buffer, later launches record into it;
+  // enable == 0: copy up to `words` words to `out` (host) and disarm.
+  if (enable) {
+    if (!g_trace_buffer) {
+      cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&g_trace_buffer), kTraceWords * 8);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return (int)cudaMemset(g_trace_buffer, 0, kTraceWords * 8);
+  }
+  if (!g_trace_buffer) return MMBO_OK;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess && out) e = cudaMemcpy(out, g_trace_buffer, (words < kTraceWords ? words : kTraceWords) * 8, cudaMemcpyDeviceToHost);
+  cudaFree(g_trace_buffer);
+  g_trace_buffer = nullptr;
+  return (int)e;
 }
 
 int mmbo_device_status(unsigned int* status) {

@@ -167,6 +167,15 @@ int mmbo_gemm_f32_noalloc(int transA, int transB, size_t m, size_t n, size_t k, 
                           const float* A, size_t lda, const float* B, size_t ldb, const float* beta,
                           float* C, size_t ldc, void* stream);
 
+/* Performance tracing of the tensor-core kernels (the device-side counterpart of the
+ * reference's -DDEBUG prints, src/gemm/driver.h:38-55).  mmbo_debug_trace(1, NULL, 0) arms
+ * a device buffer; the following HGEMM launches record clock stamps of CTA 0 for their
+ * first 64 tiles (16 words per tile: 0 tile start, 1 C requests issued, 2 accumulator
+ * ready, 3 accumulator released, 4 old C arrived, 5/6 chunk stored, 8 issuer starts waiting
+ * for a free accumulator, 9 got it, 10 all UMMAs issued).  mmbo_debug_trace(0, out, words)
+ * copies the buffer to host memory and disarms. */
+int mmbo_debug_trace(int enable, unsigned long long* out, size_t words);
+
 /* Reads and clears the device status word of the current device (synchronises the
  * device).  *status = 0 when no kernel has recorded a fault since the last call;
  * otherwise (code << 24) | detail of the first one.  Returns MMBO_OK, a CUDA error, or
