@@ -46,6 +46,7 @@ SIGNATURES = {
                                      ctypes.c_float, _sz, _sz, _sz, _vp]),
     "mmbo_device_status": (ctypes.c_int, [_u32p]),
     "mmbo_debug_trace": (ctypes.c_int, [ctypes.c_int, _vp, _sz]),
+    "mmbo_selftest_bounded_wait": (ctypes.c_int, [ctypes.c_ulonglong, _vp]),
     "mmbo_gemm_workspace_bytes": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _szp]),
     "mmbo_set_workspace": (ctypes.c_int, [_vp, _sz]),
     "mmbo_gemm_f32_noalloc": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,

@@ -165,6 +165,20 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem_byt
   return r == CUDA_SUCCESS ? MMBO_OK : MMBO_ERR_TENSOR_MAP;
 }
 
+// Self-test of the bounded-wait machinery: one thread waits on a barrier that nothing
+// will ever complete, with a short limit; it must give up, record its fault code and
+// return, leaving the context usable.
+__global__ void bounded_wait_selftest_kernel(unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0u;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+    mbar_wait(smem_u32(&bar), 0u, &abort_flag, kFaultWaitPeer, 0x5e1f, limit_ns);
+  }
+}
+
 // Device buffer for the optional event trace of the tcgen05 kernels (see trace_stamp).
 static unsigned long long* g_trace_buffer = nullptr;
 constexpr size_t kTraceWords = 64 * 16;
@@ -889,6 +903,12 @@ int mmbo_set_workspace(void* ptr, size_t bytes) {
   w.bytes = ptr ? bytes : 0;
   w.user = ptr != nullptr;
   return MMBO_OK;
+}
+
+int mmbo_selftest_bounded_wait(unsigned long long limit_ns, void* stream) {
+  if (limit_ns == 0 || limit_ns > 1000000000ull) return MMBO_ERR_BAD_DIM;
+  bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns);
+  return (int)cudaGetLastError();
 }
 
 int mmbo_debug_trace(int enable, unsigned long long* out, size_t words) {

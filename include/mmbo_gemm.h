@@ -167,6 +167,13 @@ int mmbo_gemm_f32_noalloc(int transA, int transB, size_t m, size_t n, size_t k, 
                           const float* A, size_t lda, const float* B, size_t ldb, const float* beta,
                           float* C, size_t ldc, void* stream);
 
+/* Self-test of the time-out path every barrier wait in the tensor-core kernels has:
+ * launches one thread that waits, for at most limit_ns (<= 1 s), on a barrier nothing
+ * completes.  The wait must run out, the kernel must return, and mmbo_device_status must
+ * then report fault code 7 with detail 0x5e1f.  (The reference has no failure handling
+ * beyond printing a status and exit(0): src/gemm/common.h:20-24.) */
+int mmbo_selftest_bounded_wait(unsigned long long limit_ns, void* stream);
+
 /* Performance tracing of the tensor-core kernels (the device-side counterpart of the
  * reference's -DDEBUG prints, src/gemm/driver.h:38-55).  mmbo_debug_trace(1, NULL, 0) arms
  * a device buffer; the following HGEMM launches record clock stamps of CTA 0 for their
