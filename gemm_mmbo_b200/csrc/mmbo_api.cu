@@ -486,7 +486,10 @@ static int select_f32(const GemmArgs& g) {
 }
 
 static int select_f16(const GemmArgs& g) {
-  if (!hgemm_tma_ok(g)) return 0;
+  if (g.k == 0) return 0;
+  // Operands TMA cannot address are realigned through scratch first; that only pays off
+  // once the product dwarfs the copies.
+  if (!hgemm_tma_ok(g) && (double)g.m * (double)g.n * (double)g.k < 256.0 * 256.0 * 256.0) return 0;
   // Score = fraction of the machine kept busy over whole waves of tiles x relative
   // speed of the kernel on a full wave (measured on 8192^3).
   const double sms = (double)sm_count();
@@ -555,23 +558,51 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
   return (int)cudaGetLastError();
 }
 
-static int run_f16(const GemmArgs& g, int id, cudaStream_t st) {
-  if (g.m == 0 || g.n == 0) return MMBO_OK;
-  if (g.k == 0) return launch_scale<__half>(g, st);
+// fp16 operands TMA cannot address (base not 16-byte aligned or leading dimension not a
+// multiple of 8) are first copied, column by column, into scratch with an aligned pitch
+// (a strided device-to-device copy, no arithmetic), then the tensor-core kernel runs on
+// the copies.  C needs no copy: the epilogue without TMA handles any C.
+static int realign_f16(GemmArgs& g, cudaStream_t st) {
+  const bool a_ok = aligned16(g.A) && g.lda % 8 == 0, b_ok = aligned16(g.B) && g.ldb % 8 == 0;
+  if (a_ok && b_ok) return MMBO_OK;
+  const size_t rowsA = g.transA ? g.k : g.m, colsA = g.transA ? g.m : g.k;
+  const size_t rowsB = g.transB ? g.n : g.k, colsB = g.transB ? g.k : g.n;
+  const size_t nlda = align_up(rowsA, 8), nldb = align_up(rowsB, 8);
+  const size_t a_bytes = a_ok ? 0 : align_up(nlda * colsA * 2, 1024);
+  const size_t b_bytes = b_ok ? 0 : align_up(nldb * colsB * 2, 1024);
+  void* scratch = nullptr;
+  int rc = ensure_workspace(a_bytes + b_bytes, &scratch);
+  if (rc) return rc;
+  char* base = static_cast<char*>(scratch);
+  cudaError_t e;
+  if (!a_ok) {
+    e = cudaMemcpy2DAsync(base, nlda * 2, g.A, g.lda * 2, rowsA * 2, colsA, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return (int)e;
+    g.A = base;
+    g.lda = nlda;
+  }
+  if (!b_ok) {
+    e = cudaMemcpy2DAsync(base + a_bytes, nldb * 2, g.B, g.ldb * 2, rowsB * 2, colsB, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return (int)e;
+    g.B = base + a_bytes;
+    g.ldb = nldb;
+  }
+  return MMBO_OK;
+}
+
+static int run_f16(const GemmArgs& g_in, int id, cudaStream_t st) {
+  if (g_in.m == 0 || g_in.n == 0) return MMBO_OK;
+  if (g_in.k == 0) return launch_scale<__half>(g_in, st);
+  if (id == 0) return launch_simple<__half>(g_in, st);
+  if (id < 0 || id >= kNumF16) return MMBO_ERR_BAD_KERNEL_ID;
+  GemmArgs g = g_in;
+  const int rc = realign_f16(g, st);
+  if (rc) return rc;
   switch (id) {
-    case 0: return launch_simple<__half>(g, st);
-    case 1:
-      if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
-      return launch_hgemm_tcgen05<256, 4, 1>(g, env_u32("MMBO_WGM", kF16Rows[1].wgm), st);
-    case 2:
-      if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
-      return launch_hgemm_tcgen05<128, 6, 1>(g, env_u32("MMBO_WGM", kF16Rows[2].wgm), st);
-    case 3:
-      if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
-      return launch_hgemm_tcgen05<256, 6, 2>(g, env_u32("MMBO_WGM", kF16Rows[3].wgm), st);
-    case 4:
-      if (!hgemm_tma_ok(g)) return MMBO_ERR_KERNEL_UNSUITABLE;
-      return launch_hgemm_tcgen05<256, 5, 2, 8>(g, env_u32("MMBO_WGM", kF16Rows[4].wgm), st);
+    case 1: return launch_hgemm_tcgen05<256, 4, 1>(g, env_u32("MMBO_WGM", kF16Rows[1].wgm), st);
+    case 2: return launch_hgemm_tcgen05<128, 6, 1>(g, env_u32("MMBO_WGM", kF16Rows[2].wgm), st);
+    case 3: return launch_hgemm_tcgen05<256, 6, 2>(g, env_u32("MMBO_WGM", kF16Rows[3].wgm), st);
+    case 4: return launch_hgemm_tcgen05<256, 5, 2, 8>(g, env_u32("MMBO_WGM", kF16Rows[4].wgm), st);
   }
   return MMBO_ERR_BAD_KERNEL_ID;
 }
@@ -887,6 +918,10 @@ int mmbo_gemm_workspace_bytes(int dtype, int kernelId, size_t m, size_t n, size_
   if (kernelId < 0 || kernelId >= count) return MMBO_ERR_BAD_KERNEL_ID;
   *bytes = 0;
   if (dtype == MMBO_DTYPE_F32 && (kernelId == 3 || kernelId == 4) && m && n && k) *bytes = tf32_scratch(m, n, k).total;
+  // fp16 tensor-core rows: worst case, both operands need an aligned copy
+  if (dtype == MMBO_DTYPE_F16 && kernelId >= 1 && m && n && k)
+    *bytes = align_up(align_up(m > k ? m : k, 8) * (m > k ? m : k) * 2, 1024) +
+             align_up(align_up(n > k ? n : k, 8) * (n > k ? n : k) * 2, 1024);
   return MMBO_OK;
 }
 

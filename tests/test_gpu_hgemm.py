@@ -40,19 +40,50 @@ def test_hgemm_many_tiles_per_cta(cuda, mm, oracle, kernel_id):
     run_and_check(cuda, mm, case, kernel_id)
 
 
-def test_hgemm_unaligned_operands_take_the_general_path(cuda, mm, oracle):
-    """Leading dimensions that are not multiples of 8 cannot be described to TMA; the
-    automatic choice must fall back and a forced tensor-core kernel must refuse."""
-    case = Case(oracle, "f16", False, True, 100, 60, 50, 1.0, 0.5, pad=(3, 3, 3))
-    run_and_check(cuda, mm, case, -1)
+def test_hgemm_unaligned_operands(cuda, mm, oracle):
+    """Leading dimensions that are not multiples of 8 cannot be described to TMA: small
+    problems take the general kernel, large ones (and forced tensor-core rows) are realigned
+    through scratch and run on the tensor cores; results are the same either way."""
     from helpers import to_device
-    _, dA = to_device(cuda, case.A)
-    _, dB = to_device(cuda, case.B)
-    _, dC = to_device(cuda, case.C)
-    assert mm.select_kernel("f16", False, True, 100, 60, 50, dA, case.lda, dB, case.ldb, dC, case.ldc) == 0
-    with pytest.raises(mm.MmboError) as e:
-        mm.gemm("f16", False, True, 100, 60, 50, 1.0, dA, case.lda, dB, case.ldb, 0.5, dC, case.ldc, 1)
-    assert e.value.status == -8
+    small = Case(oracle, "f16", False, True, 100, 60, 50, 1.0, 0.5, pad=(3, 3, 3))
+    _, dA = to_device(cuda, small.A)
+    _, dB = to_device(cuda, small.B)
+    _, dC = to_device(cuda, small.C)
+    assert mm.select_kernel("f16", False, True, 100, 60, 50, dA, small.lda, dB, small.ldb, dC, small.ldc) == 0
+    for kid in (-1, 1, 2, 3, 4):
+        run_and_check(cuda, mm, small, kid)
+    for ta, tb in MODES:
+        big = Case(oracle, "f16", ta, tb, 515, 389, 301, 1.0, 0.5, pad=(1, 3, 5), dist=oracle.DIST_NORMAL, scale=0.5)
+        _, dA = to_device(cuda, big.A)
+        _, dB = to_device(cuda, big.B)
+        _, dC = to_device(cuda, big.C)
+        assert mm.select_kernel("f16", ta, tb, 515, 389, 301, dA, big.lda, dB, big.ldb, dC, big.ldc) != 0
+        for kid in (-1, 3, 4):
+            run_and_check(cuda, mm, big, kid)
+
+
+def test_hgemm_misaligned_base_pointers(cuda, mm, oracle):
+    """A, B, C that start 2 bytes off a 16-byte boundary (sub-matrix views into a larger
+    allocation) under otherwise TMA-friendly leading dimensions."""
+    import numpy as np
+    torch = cuda
+    m, n, k = 520, 392, 328
+    case = Case(oracle, "f16", False, True, m, n, k, 1.0, 0.5, pad=(8, 8, 8), dist=oracle.DIST_NORMAL, scale=0.5)
+    devs = []
+    for host in (case.A, case.B, case.C):
+        buf = torch.zeros(host.size + 1, dtype=torch.float16, device="cuda")
+        buf[1:].copy_(torch.from_numpy(host.reshape(-1)))
+        devs.append(buf)
+    dA, dB, dC = (b[1:] for b in devs)
+    assert dA.data_ptr() % 16 == 2
+    mm.gemm("f16", False, True, m, n, k, 1.0, dA, case.lda, dB, case.ldb, 0.5, dC, case.ldc, 3)
+    torch.cuda.synchronize()
+    assert mm.device_status() == 0
+    got = dC.cpu().numpy().reshape(case.C.shape)
+    assert np.array_equal(got[:, m:].view(np.uint16), case.C[:, m:].view(np.uint16))
+    assert float(devs[2][0]) == 0.0  # the element before C untouched
+    err = oracle.rel_frobenius("f16", m, n, np.ascontiguousarray(got), case.ldc, case.reference())
+    assert err <= 2e-3, err
 
 
 def test_hgemm_k_zero_and_empty(cuda, mm, oracle):
