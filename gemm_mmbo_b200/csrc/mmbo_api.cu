@@ -11,6 +11,7 @@
 #include <string.h>
 
 #include "../../include/mmbo_gemm.h"
+#include "dgemm_dmma.cuh"
 #include "dgemm_fma.cuh"
 #include "hgemm_tcgen05.cuh"
 #include "ref_kernels.cuh"
@@ -33,6 +34,7 @@ static const KernelRow kF32Rows[] = {
     {"sgemm_ffma_MT064x064x16_TT04_04_WG256_WGM08", 64, 64, 256, 16, 2, 1, 8, 0},
     {"sgemm_tf32x3_tcgen05_MT128x256x32_S4_CG2_WG192_WGM08", 128, 256, 192, 32, 4, 2, 8, 1},
     {"sgemm_tf32x3_tcgen05_MT128x128x32_S3_CG1_WG192_WGM08", 128, 128, 192, 32, 3, 1, 8, 1},
+    {"sgemm_tf32x3_tcgen05_MT256x256x32_S3_CG2_WG384_WGM08", 256, 256, 384, 32, 3, 2, 8, 1},
 };
 // fp16 rows: MT<tile m>x<tile n>x<DepthU>_S<stages>_CG<cta group>.
 static const KernelRow kF16Rows[] = {
@@ -46,6 +48,7 @@ static const KernelRow kF16Rows[] = {
 static const KernelRow kF64Rows[] = {
     {"dgemm_simple_MT032x008x01_TT01_01_WG256", 32, 8, 256, 1, 1, 1, 1, 0},
     {"dgemm_fma_MT064x064x16_TT04_04_WG256_WGM08", 64, 64, 256, 16, 2, 1, 8, 0},
+    {"dgemm_dmma_MT128x064x08_WT32_32_WG256_WGM08", 128, 64, 256, 8, 2, 1, 8, 1},
 };
 constexpr int kNumF64 = sizeof(kF64Rows) / sizeof(KernelRow);
 constexpr int kNumF32 = sizeof(kF32Rows) / sizeof(KernelRow);
@@ -377,11 +380,11 @@ static Tf32Scratch tf32_scratch(size_t m, size_t n, size_t k) {
   return s;
 }
 
-template <int TM, int STAGES, int CG>
+template <int TM, int STAGES, int CG, int EW>
 static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float* a_lo, const float* b_hi,
                               const float* b_lo, size_t kpad, uint32_t wgm, cudaStream_t st) {
-  using L = TfSmem<TM, STAGES, CG>;
-  auto kern = sgemm_tf32x3_kernel<TM, STAGES, CG>;
+  using L = TfSmem<TM, STAGES, CG, EW>;
+  auto kern = sgemm_tf32x3_kernel<TM, STAGES, CG, EW>;
   CUtensorMap ta_hi, ta_lo, tb_hi, tb_lo, tc;
   int rc;
   if ((rc = make_map_2d(&ta_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a_hi, g.k, g.m, kpad, kTfBlockK, TM / CG))) return rc;
@@ -418,7 +421,7 @@ static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float*
     if (CG == 2) {
       cudaLaunchConfig_t q = {};
       q.gridDim = dim3((unsigned)(2 * walkers));
-      q.blockDim = dim3(kTfThreads);
+      q.blockDim = dim3(L::kThreads);
       q.dynamicSmemBytes = L::kDynamic;
       cudaLaunchAttribute qa[1];
       qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -434,7 +437,7 @@ static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float*
   const unsigned walkers = (unsigned)(tiles < (uint64_t)max_walkers[dev] ? tiles : (uint64_t)max_walkers[dev]);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(walkers * CG);
-  cfg.blockDim = dim3(kTfThreads);
+  cfg.blockDim = dim3(L::kThreads);
   cfg.dynamicSmemBytes = L::kDynamic;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -445,7 +448,7 @@ static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float*
 }
 
 // Split + repack of both operands into `scratch`, then the tensor-core GEMM.
-template <int TM, int STAGES, int CG>
+template <int TM, int STAGES, int CG, int EW = 4>
 static int run_tf32x3(const GemmArgs& g, void* scratch, uint32_t wgm, cudaStream_t st) {
   const Tf32Scratch s = tf32_scratch(g.m, g.n, g.k);
   if (((g.m + 31) / 32) > 65535 || ((g.n + 31) / 32) > 65535) return MMBO_ERR_TOO_LARGE;
@@ -467,7 +470,7 @@ static int run_tf32x3(const GemmArgs& g, void* scratch, uint32_t wgm, cudaStream
   else split_pack_kernel<false><<<grid_b, block, 0, st>>>(B, g.ldb, (uint32_t)g.n, (uint32_t)g.k, (uint32_t)s.kpad, b_hi, b_lo);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  return launch_tf32x3_gemm<TM, STAGES, CG>(g, a_hi, a_lo, b_hi, b_lo, s.kpad, wgm, st);
+  return launch_tf32x3_gemm<TM, STAGES, CG, EW>(g, a_hi, a_lo, b_hi, b_lo, s.kpad, wgm, st);
 }
 
 // ------------------------------------------------------------------ selection --------
@@ -478,6 +481,8 @@ static int select_f32(const GemmArgs& g) {
   // MMBO_F32_EXACT=1 keeps automatic selection on the CUDA-core kernels.
   const double work = (double)g.m * (double)g.n * (double)g.k;
   if (work >= 512.0 * 512.0 * 512.0 && env_u32("MMBO_F32_EXACT", 0) == 0) {
+    const uint64_t big_pairs = (uint64_t)((g.m + 255) / 256) * ((g.n + 255) / 256);
+    if (big_pairs >= 2ull * (uint64_t)(sm_count() / 2)) return 5;  // 256 x 256 tiles, two waves or more
     const uint64_t pair_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 255) / 256);
     return pair_tiles >= (uint64_t)(sm_count() / 2) ? 3 : 4;
   }
@@ -519,11 +524,13 @@ static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
     case 1: return launch_sgemm_ffma<128, 128, 8, 8>(g, env_u32("MMBO_WGM", kF32Rows[1].wgm), st);
     case 2: return launch_sgemm_ffma<64, 64, 4, 4>(g, env_u32("MMBO_WGM", kF32Rows[2].wgm), st);
     case 3:
-    case 4: {
+    case 4:
+    case 5: {
       void* scratch = nullptr;
       const int rc = ensure_workspace(tf32_scratch(g.m, g.n, g.k).total, &scratch);
       if (rc) return rc;
       if (id == 3) return run_tf32x3<128, 4, 2>(g, scratch, env_u32("MMBO_WGM", kF32Rows[3].wgm), st);
+      if (id == 5) return run_tf32x3<256, 3, 2, 8>(g, scratch, env_u32("MMBO_WGM", kF32Rows[5].wgm), st);
       return run_tf32x3<128, 3, 1>(g, scratch, env_u32("MMBO_WGM", kF32Rows[4].wgm), st);
     }
   }
@@ -543,11 +550,21 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
     else gemm_simple_f64_kernel<<<grid, block, 0, st>>>(g.transA, g.transB, g.m, g.n, g.k, alpha, A, g.lda, B, g.ldb, beta, C, g.ldc);
     return (int)cudaGetLastError();
   }
-  if (id != 1) return MMBO_ERR_BAD_KERNEL_ID;
+  if (id != 1 && id != 2) return MMBO_ERR_BAD_KERNEL_ID;
   DgemmParams p;
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
   p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
-  p.alpha = alpha; p.beta = beta; p.wgm = env_u32("MMBO_WGM", kF64Rows[1].wgm);
+  p.alpha = alpha; p.beta = beta; p.wgm = env_u32("MMBO_WGM", kF64Rows[id].wgm);
+  if (id == 2) {  // fp64 tensor path
+    const size_t gx2 = (g.m + kDmBM - 1) / kDmBM, gy2 = (g.n + kDmBN - 1) / kDmBN;
+    if (gy2 > 65535) return MMBO_ERR_TOO_LARGE;
+    dim3 grid2((unsigned)gx2, (unsigned)gy2);
+    if (!g.transA && !g.transB) dgemm_dmma_kernel<false, false><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
+    else if (!g.transA && g.transB) dgemm_dmma_kernel<false, true><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
+    else if (g.transA && !g.transB) dgemm_dmma_kernel<true, false><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
+    else dgemm_dmma_kernel<true, true><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
+    return (int)cudaGetLastError();
+  }
   const size_t gx = (g.m + kDgBM - 1) / kDgBM, gy = (g.n + kDgBN - 1) / kDgBN;
   if (gy > 65535) return MMBO_ERR_TOO_LARGE;
   dim3 grid((unsigned)gx, (unsigned)gy);
@@ -787,7 +804,7 @@ int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const do
   int rc = validate(g, reinterpret_cast<const float*>(alpha), reinterpret_cast<const float*>(beta));
   if (rc) return rc;
   if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF64)) return MMBO_ERR_BAD_KERNEL_ID;
-  const int id = kernelId == MMBO_KERNEL_AUTO ? 1 : kernelId;
+  const int id = kernelId == MMBO_KERNEL_AUTO ? 2 : kernelId;  // the fp64 tensor path
   return run_f64(g, *alpha, *beta, id, static_cast<cudaStream_t>(stream));
 }
 
@@ -824,7 +841,7 @@ int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, si
   if (rc) return rc;
   if (dtype == MMBO_DTYPE_F32) return select_f32(g);
   if (dtype == MMBO_DTYPE_F16) return select_f16(g);
-  if (dtype == MMBO_DTYPE_F64) return g.k == 0 ? 0 : 1;
+  if (dtype == MMBO_DTYPE_F64) return g.k == 0 ? 0 : 2;
   return MMBO_ERR_BAD_DTYPE;
 }
 
@@ -917,7 +934,7 @@ int mmbo_gemm_workspace_bytes(int dtype, int kernelId, size_t m, size_t n, size_
   if (!rows_of(dtype, &count)) return MMBO_ERR_BAD_DTYPE;
   if (kernelId < 0 || kernelId >= count) return MMBO_ERR_BAD_KERNEL_ID;
   *bytes = 0;
-  if (dtype == MMBO_DTYPE_F32 && (kernelId == 3 || kernelId == 4) && m && n && k) *bytes = tf32_scratch(m, n, k).total;
+  if (dtype == MMBO_DTYPE_F32 && kernelId >= 3 && kernelId <= 5 && m && n && k) *bytes = tf32_scratch(m, n, k).total;
   // fp16 tensor-core rows: worst case, both operands need an aligned copy
   if (dtype == MMBO_DTYPE_F16 && kernelId >= 1 && m && n && k)
     *bytes = align_up(align_up(m > k ? m : k, 8) * (m > k ? m : k) * 2, 1024) +

@@ -77,20 +77,26 @@ split_pack_kernel(const float* __restrict__ X, size_t ld, uint32_t R, uint32_t K
 constexpr int kTfTileN = 128;  // problem-N extent per CTA = UMMA M per CTA
 constexpr int kTfBlockK = 32;  // floats per stage along K = one 128-byte swizzle row
 constexpr int kTfUmmaK = 8;    // K extent of one kind::tf32 UMMA
-constexpr int kTfThreads = 192;
 constexpr int kTfEpiBufBytes = 32 * 128;  // 32 C columns x 32 rows of fp32
-constexpr int kTfTileM = 128;  // problem-M extent of a tile = UMMA N = running sums per epilogue thread
+constexpr int kTfSums = 128;   // running sums (accumulator columns) one epilogue thread keeps in registers
 
-template <int TM, int STAGES, int CG>
+// EW epilogue warps: 4 (tile of 128 rows of C: every warp owns all 128 accumulator columns
+// of its lane quarter) or 8 (tile of 256 rows: two warps per quarter, 128 columns each).
+// With 8 the block has three warpgroups -- {producer, issuer, 2 idle warps}, {4 epilogue
+// warps}, {4 epilogue warps} -- so that the first can hand registers to the other two.
+template <int TM, int STAGES, int CG, int EW = 4>
 struct TfSmem {
+  static constexpr int kThreads = EW == 4 ? 192 : 384;
+  static constexpr int kFirstEpiWarp = EW == 4 ? 2 : 4;
+  static constexpr int kBufsPerWarp = EW == 4 ? 2 : 1;
   static constexpr int kAopRows = TM / CG;
   static constexpr int kBopBytes = kTfTileN * 128;  // one of hi / lo
   static constexpr int kAopBytes = kAopRows * 128;
   static constexpr int kStageBytes = 2 * (kBopBytes + kAopBytes);  // Bhi, Blo, Ahi, Alo
   static constexpr int kEpiOffset = STAGES * kStageBytes;
-  static constexpr int kEpiBytes = 4 * 2 * kTfEpiBufBytes;
+  static constexpr int kEpiBytes = EW * kBufsPerWarp * kTfEpiBufBytes;
   static constexpr int kBarOffset = kEpiOffset + kEpiBytes;
-  static constexpr int kNumBars = 2 * STAGES + 4 + 8;
+  static constexpr int kNumBars = 2 * STAGES + 4 + 2 * EW;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
   static constexpr int kTotal = kMiscOffset + 16;
   static constexpr int kDynamic = kTotal + 1024;
@@ -107,13 +113,13 @@ struct TfParams {
   uint32_t chunk;  // stages accumulated in tensor memory before the partial sum is drained
 };
 
-template <int TM, int STAGES, int CG>
-__global__ void __launch_bounds__(kTfThreads, 1)
+template <int TM, int STAGES, int CG, int EW = 4>
+__global__ void __launch_bounds__(EW == 4 ? 192 : 384, 1)
 sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_constant__ CUtensorMap tmap_a_lo,
                     const __grid_constant__ CUtensorMap tmap_b_hi, const __grid_constant__ CUtensorMap tmap_b_lo,
                     const __grid_constant__ CUtensorMap tmap_c, const TfParams p) {
-  using L = TfSmem<TM, STAGES, CG>;
-  static_assert(TM == kTfTileM, "one epilogue thread keeps TM running sums in registers");
+  using L = TfSmem<TM, STAGES, CG, EW>;
+  static_assert(TM == kTfSums * (EW / 4), "one epilogue thread keeps 128 running sums in registers");
   constexpr uint32_t kTmemCols = 2 * TM;  // two partial-sum buffers
 
   extern __shared__ uint8_t smem_raw[];
@@ -143,9 +149,9 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
     }
     for (uint32_t a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 4 * CG);
+      mbar_init(tmem_empty_bar(a), EW * CG);
     }
-    for (uint32_t w = 0; w < 4; ++w)
+    for (uint32_t w = 0; w < EW; ++w)
       for (uint32_t b = 0; b < 2; ++b) mbar_init(cload_bar(w, b), 1);
     fence_mbar_init();
     prefetch_tensormap(&tmap_a_hi);
@@ -168,7 +174,12 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
 
+  // With 8 epilogue warps (384 threads, 168 registers each at launch) the first warpgroup
+  // hands registers to the two epilogue warpgroups, whose threads keep 128 running sums:
+  // 56 / 224 / 224.  Each role branch opens with its own setmaxnreg so that the
+  // assembler allocates registers per branch.
   if (warp == 0) {
+    if constexpr (EW == 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     // ===== TMA producer =====
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, issued = 0;
@@ -219,6 +230,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
     }
     __syncwarp();
   } else if (warp == 1) {
+    if constexpr (EW == 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     // ===== UMMA issuer (leader CTA of a pair) =====
     if (lane == 0 && cta_rank == 0) {
       constexpr uint32_t idesc = make_idesc(2u, 0u, 0u, kTfTileN * CG, TM);
@@ -272,11 +284,16 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
       }
     }
     __syncwarp();
+  } else if (warp < L::kFirstEpiWarp) {
+    if constexpr (EW == 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");  // idle warps of the first warpgroup
   } else {
-    // ===== epilogue: warp owns tensor-memory lanes [32q, 32q+32) = 32 columns of C =====
-    const uint32_t q = warp & 3u, epi_w = warp - 2u;
-    const uint32_t buf_base = smem_base + L::kEpiOffset + epi_w * 2u * kTfEpiBufBytes;
-    uint8_t* buf_gen = smem_gen + L::kEpiOffset + epi_w * 2u * kTfEpiBufBytes;
+    if constexpr (EW == 8) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    // ===== epilogue: warp owns tensor-memory lanes [32q, 32q+32) = 32 columns of C and
+    // 128 accumulator columns (= rows of C) of them =====
+    const uint32_t q = warp & 3u, epi_w = warp - L::kFirstEpiWarp;
+    const uint32_t col_base = (epi_w >> 2) * kTfSums;
+    const uint32_t buf_base = smem_base + L::kEpiOffset + epi_w * L::kBufsPerWarp * kTfEpiBufBytes;
+    uint8_t* buf_gen = smem_gen + L::kEpiOffset + epi_w * L::kBufsPerWarp * kTfEpiBufBytes;
     const bool use_c = (p.beta != 0.0f);
     const bool c_tma = p.c_tma != 0u;
     const float alpha = p.alpha, beta = p.beta;
@@ -287,29 +304,29 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
     for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers) {
       uint32_t tm_idx, tn_idx;
       mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
-      const uint32_t m0 = tm_idx * TM;
+      const uint32_t m0 = tm_idx * TM + col_base;
       const uint32_t ncol0 = (tn_idx * CG + cta_rank) * kTfTileN + 32u * q;
       // running sums of this thread's C column over the tile's TM rows
-      float sums[TM];
+      float sums[kTfSums];
 #pragma unroll
-      for (int i = 0; i < TM; ++i) sums[i] = 0.f;
+      for (int i = 0; i < kTfSums; ++i) sums[i] = 0.f;
       for (uint32_t ch = 0; ok && ch < num_chunks; ++ch, ++chunk_ctr) {
         const uint32_t acc = chunk_ctr & 1u, acc_phase = (chunk_ctr >> 1) & 1u;
         ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, kFaultWaitTmemFull, acc));
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t t_warp = tmem_base + ((32u * q) << 16) + acc * TM;
+        const uint32_t t_warp = tmem_base + ((32u * q) << 16) + acc * TM + col_base;
         // two register buffers: the load of columns c+1 is in flight during the adds of c
         uint32_t r0[32], r1[32];
         tmem_ld_32x32(t_warp, r0);
 #pragma unroll
-        for (uint32_t c = 0; c < TM / 32; c += 2) {
+        for (uint32_t c = 0; c < kTfSums / 32; c += 2) {
           tmem_ld_wait();
           tmem_ld_32x32(t_warp + 32u * (c + 1), r1);
 #pragma unroll
           for (int e = 0; e < 32; ++e) sums[32 * c + e] += __uint_as_float(r0[e]);
           tmem_ld_wait();
-          if (c + 2 < TM / 32) tmem_ld_32x32(t_warp + 32u * (c + 2), r0);
+          if (c + 2 < kTfSums / 32) tmem_ld_32x32(t_warp + 32u * (c + 2), r0);
 #pragma unroll
           for (int e = 0; e < 32; ++e) sums[32 * (c + 1) + e] += __uint_as_float(r1[e]);
         }
@@ -323,8 +340,8 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
       }
       if (!ok) break;
 #pragma unroll
-      for (uint32_t c = 0; c < TM / 32; ++c, ++out_ctr) {
-        const uint32_t b = out_ctr & 1u;
+      for (uint32_t c = 0; c < kTfSums / 32; ++c, ++out_ctr) {
+        const uint32_t b = L::kBufsPerWarp == 2 ? (out_ctr & 1u) : 0u;
         const uint32_t sbuf = buf_base + b * kTfEpiBufBytes;
         float* gbuf = reinterpret_cast<float*>(buf_gen + b * kTfEpiBufBytes);
         const uint32_t mrow0 = m0 + 32u * c;
@@ -333,7 +350,10 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
         // staging tile: row t = C column ncol0 + t, 32 floats = rows mrow0 .. mrow0+31;
         // 16-byte piece j of a row lives at piece (j ^ (t & 7)) (the 128-byte TMA swizzle)
         if (c_tma) {
-          if (lane == 0) tma_store_wait_read<1>();  // this buffer's previous store has read it
+          if (lane == 0) {  // this buffer's previous store has read it
+            if constexpr (L::kBufsPerWarp == 2) tma_store_wait_read<1>();
+            else tma_store_wait_read<0>();
+          }
           __syncwarp();
           if (load_c && lane == 0) {
             mbar_expect_tx(cload_bar(epi_w, b), kTfEpiBufBytes);

@@ -11,7 +11,7 @@ MODES = [(False, False), (False, True), (True, False), (True, True)]
 SHAPES = [(1, 1, 1), (5, 3, 2), (64, 64, 16), (65, 63, 17), (129, 127, 33), (200, 300, 100), (257, 130, 129)]
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, -1])
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_dgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
     for (m, n, k) in SHAPES:
@@ -20,7 +20,7 @@ def test_dgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
             run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2])
 def test_dgemm_beta_zero_and_k_zero(cuda, mm, oracle, kernel_id):
     run_and_check(cuda, mm, Case(oracle, "f64", False, True, 150, 70, 40, 2.0, 0.0, pad=(1, 2, 3), c_poison=True),
                   kernel_id)

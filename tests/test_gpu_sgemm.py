@@ -14,7 +14,7 @@ SHAPES = [(1, 1, 1), (5, 3, 2), (64, 64, 16), (65, 63, 17), (128, 128, 32), (129
           (200, 300, 100), (384, 256, 64), (257, 513, 129)]
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, 5, -1])
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_sgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
     for (m, n, k) in SHAPES:
@@ -23,13 +23,13 @@ def test_sgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
             run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, 5, -1])
 def test_sgemm_beta_zero_never_reads_c(cuda, mm, oracle, kernel_id):
     case = Case(oracle, "f32", False, True, 150, 70, 40, 2.0, 0.0, pad=(1, 2, 3), c_poison=True)
     run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, 5, -1])
 def test_sgemm_k_zero_scales_c(cuda, mm, oracle, kernel_id):
     case = Case(oracle, "f32", False, False, 70, 33, 0, 2.0, 0.5, pad=(0, 0, 5))
     run_and_check(cuda, mm, case, kernel_id)
@@ -65,7 +65,7 @@ def test_sgemm_tf32x3_accuracy_large_k(cuda, mm, oracle):
     contraction (k = 8192): relative Frobenius error <= 1e-5, like the FFMA kernels."""
     case = Case(oracle, "f32", True, False, 384, 320, 8192, 1.0, 0.5)
     ref = case.reference()
-    errs = {kid: run_and_check(cuda, mm, case, kid, ref=ref) for kid in (1, 3, 4)}
+    errs = {kid: run_and_check(cuda, mm, case, kid, ref=ref) for kid in (1, 3, 4, 5)}
     print("rel Frobenius:", errs)
     assert max(errs.values()) <= 1e-5
 
