@@ -32,12 +32,17 @@ SIGNATURES = {
                                           _fp, _vp, _sz, ctypes.c_int]),
     "mmbo_gemm_f16_host": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
                                           _fp, _vp, _sz, ctypes.c_int]),
+    "mmbo_gemm_strided_batched": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _vp, _vp,
+                                                 _sz, _sz, _vp, _sz, _sz, _vp, _vp, _sz, _sz, _sz, ctypes.c_int, _vp]),
     "mmbo_num_kernels": (ctypes.c_int, [ctypes.c_int]),
     "mmbo_kernel_name": (ctypes.c_char_p, [ctypes.c_int, ctypes.c_int]),
     "mmbo_kernel_params": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]),
     "mmbo_select_kernel": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _vp, _sz,
                                           _vp, _sz, _vp, _sz]),
     "mmbo_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "mmbo_tuning_set": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, ctypes.c_int]),
+    "mmbo_tuning_load": (ctypes.c_int, [ctypes.c_char_p]),
+    "mmbo_tuning_clear": (None, []),
     "mmbo_wgm_map": (None, [ctypes.c_uint32] * 5 + [_u32p, _u32p]),
     "mmbo_shard_columns": (ctypes.c_int, [_sz, ctypes.c_int, ctypes.c_int, _sz, _szp, _szp]),
     "mmbo_fill_f32": (ctypes.c_int, [_vp, _sz, _sz, _sz, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int,
@@ -68,3 +73,10 @@ def load() -> ctypes.CDLL:
 
 
 LIB = load()
+
+# The packaged tuning table (written by gemm_mmbo_b200.autotune on a B200) is loaded once;
+# MMBO_TUNING_FILE, when set, is read by the library itself and takes its place.
+import os as _os  # noqa: E402
+_TABLE = _PKG / "tuning" / "b200.tbl"
+if _TABLE.exists() and not _os.environ.get("MMBO_TUNING_FILE") and not _os.environ.get("MMBO_NO_TUNING"):
+    LIB.mmbo_tuning_load(str(_TABLE).encode())

@@ -1,0 +1,91 @@
+"""Brute-force kernel selection, persisted.
+
+    python -m gemm_mmbo_b200.autotune --out gemm_mmbo_b200/tuning/b200.tbl [--preset baseline,sweep] [--iters 10]
+
+For every problem of the chosen presets, every kernel id of the dtype's table is timed
+through the C ABI (CUDA events, warm-up first) and the fastest id is written as one row
+of a tuning file that `mmbo_tuning_load` / MMBO_TUNING_FILE understand.  This is the
+reference's sweep over its kernel table (src/gemm/benchmark.cc:92-106) with the result
+kept, in the spirit of its Tensile library logic, where each tuned size carries
+[solution index, GFLOP/s] (src/gemm/ref/vega20_Cijk_Ailk_Bjlk_DB.yaml:929-1177).
+"""
+from __future__ import annotations
+
+import argparse
+import pathlib
+import time
+
+
+def problems(presets: list[str]):
+    out = []
+    if "baseline" in presets:  # the benchmark configurations
+        out += [("f32", "NN", 1024, 1024, 1024), ("f16", "NT", 8192, 8192, 8192)]
+        out += [("f32", t, 4095, 4097, 1023) for t in ("NN", "NT", "TN", "TT")]
+        out += [("f16", "TN", 65536, 128, 4096), ("f16", "TN", 128, 65536, 4096), ("f16", "TN", 8192, 8192, 256)]
+        out += [("f16", "NN", 32768, 32768 // p, 32768) for p in (8, 4)]
+    if "sweep" in presets:  # the reference's run.sh sweep (M = 44160 .. 384 step -384, N = 2048, K = 384), thinned
+        for dtype in ("f16", "f32", "f64"):
+            out += [(dtype, "NT", m, 2048, 384) for m in (44160, 33408, 22272, 11136, 5376, 1536, 384)]
+    return out
+
+
+def time_kernel(mm, torch, dtype, trans, m, n, k, kid, iters):
+    ta, tb = trans[0] == "T", trans[1] == "T"
+    tdt = {"f16": torch.float16, "f32": torch.float32, "f64": torch.float64}[dtype]
+    ra, rb = (k if ta else m), (n if tb else k)
+    ca, cb = (m if ta else k), (k if tb else n)
+    A = torch.empty((ca, ra), dtype=tdt, device="cuda")
+    B = torch.empty((cb, rb), dtype=tdt, device="cuda")
+    C = torch.zeros((n, m), dtype=tdt, device="cuda")
+    mm.fill(dtype, A, ra, ca, ra, mat=0)
+    mm.fill(dtype, B, rb, cb, rb, mat=1)
+    try:
+        for _ in range(3):
+            mm.gemm(dtype, ta, tb, m, n, k, 1.0, A, ra, B, rb, 0.5, C, m, kid)
+    except mm.MmboError:
+        return None
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        mm.gemm(dtype, ta, tb, m, n, k, 1.0, A, ra, B, rb, 0.5, C, m, kid)
+    e1.record()
+    torch.cuda.synchronize()
+    if mm.device_status() != 0:
+        return None
+    return e0.elapsed_time(e1) / iters
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--preset", default="baseline,sweep")
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    import torch
+
+    import gemm_mmbo_b200 as mm
+    torch.cuda.set_device(0)
+    mm.tuning_clear()
+    lines = [f"# tuning table written by gemm_mmbo_b200.autotune on {torch.cuda.get_device_name(0)}, "
+             f"{time.strftime('%Y-%m-%d')}", "# dtype trans m n k kernelId   # best TFLOP/s (runner-up id: TFLOP/s)"]
+    for (dtype, trans, m, n, k) in problems(args.preset.split(",")):
+        results = []
+        for kid in range(mm.num_kernels(dtype)):
+            if kid == 0 and 2.0 * m * n * k > 2e11:
+                continue  # the one-thread-per-element kernel is only a candidate for tiny problems
+            ms = time_kernel(mm, torch, dtype, trans, m, n, k, kid, args.iters)
+            if ms is not None:
+                results.append((2.0 * m * n * k / ms / 1e9, kid))
+        results.sort(reverse=True)
+        best = results[0]
+        second = f" ({results[1][1]}: {results[1][0]:.1f})" if len(results) > 1 else ""
+        lines.append(f"{dtype} {trans} {m} {n} {k} {best[1]}   # {best[0]:.1f}{second}")
+        print(lines[-1], flush=True)
+    out = pathlib.Path(args.out)
+    out.parent.mkdir(parents=True, exist_ok=True)
+    out.write_text("\n".join(lines) + "\n")
+
+
+if __name__ == "__main__":
+    main()

@@ -7,6 +7,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -451,15 +452,15 @@ static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float*
 template <int TM, int STAGES, int CG, int EW = 4>
 static int run_tf32x3(const GemmArgs& g, void* scratch, uint32_t wgm, cudaStream_t st) {
   const Tf32Scratch s = tf32_scratch(g.m, g.n, g.k);
-  if (((g.m + 31) / 32) > 65535 || ((g.n + 31) / 32) > 65535) return MMBO_ERR_TOO_LARGE;
+  if (((g.m + 63) / 64) > 65535 || ((g.n + 63) / 64) > 65535) return MMBO_ERR_TOO_LARGE;
   char* base = static_cast<char*>(scratch);
   float* a_hi = reinterpret_cast<float*>(base);
   float* a_lo = reinterpret_cast<float*>(base + s.a_bytes);
   float* b_hi = reinterpret_cast<float*>(base + 2 * s.a_bytes);
   float* b_lo = reinterpret_cast<float*>(base + 2 * s.a_bytes + s.b_bytes);
-  const dim3 block(32, 8);
-  const dim3 grid_a((unsigned)((g.k + 31) / 32), (unsigned)((g.m + 31) / 32));
-  const dim3 grid_b((unsigned)((g.k + 31) / 32), (unsigned)((g.n + 31) / 32));
+  const dim3 block(256);
+  const dim3 grid_a((unsigned)((g.k + 63) / 64), (unsigned)((g.m + 63) / 64));
+  const dim3 grid_b((unsigned)((g.k + 63) / 64), (unsigned)((g.n + 63) / 64));
   const float* A = static_cast<const float*>(g.A);
   const float* B = static_cast<const float*>(g.B);
   // op(A)(i,l): row index contiguous unless transposed; op(B)(l,j) as an n x k operand:
@@ -473,9 +474,81 @@ static int run_tf32x3(const GemmArgs& g, void* scratch, uint32_t wgm, cudaStream
   return launch_tf32x3_gemm<TM, STAGES, CG, EW>(g, a_hi, a_lo, b_hi, b_lo, s.kpad, wgm, st);
 }
 
+// ------------------------------------------------------------------ tuning table -----
+// Exact-size overrides of the selection heuristics, the counterpart of the reference's
+// Tensile library logic (src/gemm/ref/vega20_Cijk_Ailk_Bjlk_DB.yaml:929-1177: one
+// [size] -> [solution index, GFLOP/s] row per tuned problem).  Rows come from
+// mmbo_tuning_set, from a file given to mmbo_tuning_load, or from the file named by the
+// environment variable MMBO_TUNING_FILE (read once, on the first automatic selection).
+// File format, one row per line, '#' starts a comment:
+//     <dtype f16|f32|f64> <trans NN|NT|TN|TT> <m> <n> <k> <kernelId>
+struct TuneRow {
+  int dtype, ta, tb;
+  size_t m, n, k;
+  int kernel;
+};
+constexpr int kMaxTuneRows = 4096;
+static TuneRow g_tune[kMaxTuneRows];
+static int g_tune_count = 0;
+static bool g_tune_env_done = false;
+
+static int tune_set(int dtype, int ta, int tb, size_t m, size_t n, size_t k, int kernel) {
+  int count = 0;
+  if (!rows_of(dtype, &count)) return MMBO_ERR_BAD_DTYPE;
+  if (kernel < 0 || kernel >= count) return MMBO_ERR_BAD_KERNEL_ID;
+  for (int i = 0; i < g_tune_count; ++i) {
+    TuneRow& r = g_tune[i];
+    if (r.dtype == dtype && r.ta == ta && r.tb == tb && r.m == m && r.n == n && r.k == k) {
+      r.kernel = kernel;
+      return MMBO_OK;
+    }
+  }
+  if (g_tune_count >= kMaxTuneRows) return MMBO_ERR_TOO_LARGE;
+  g_tune[g_tune_count++] = TuneRow{dtype, ta, tb, m, n, k, kernel};
+  return MMBO_OK;
+}
+
+static int tune_load(const char* path) {
+  FILE* f = fopen(path, "r");
+  if (!f) return MMBO_ERR_TUNING_FILE;
+  char line[256];
+  int rc = MMBO_OK;
+  while (fgets(line, sizeof line, f)) {
+    char dt[8], tr[8];
+    unsigned long long m, n, k;
+    int kernel;
+    if (line[0] == '#' || line[0] == '\n') continue;
+    if (sscanf(line, "%7s %7s %llu %llu %llu %d", dt, tr, &m, &n, &k, &kernel) != 6) { rc = MMBO_ERR_TUNING_FILE; break; }
+    const int dtype = !strcmp(dt, "f16") ? MMBO_DTYPE_F16 : !strcmp(dt, "f32") ? MMBO_DTYPE_F32
+                      : !strcmp(dt, "f64") ? MMBO_DTYPE_F64 : -1;
+    if (dtype < 0 || strlen(tr) != 2) { rc = MMBO_ERR_TUNING_FILE; break; }
+    rc = tune_set(dtype, tr[0] == 'T', tr[1] == 'T', m, n, k, kernel);
+    if (rc) break;
+  }
+  fclose(f);
+  return rc;
+}
+
+// Kernel id the table holds for this exact problem, or -1.
+static int tune_lookup(int dtype, const GemmArgs& g) {
+  if (!g_tune_env_done) {
+    g_tune_env_done = true;
+    const char* path = getenv("MMBO_TUNING_FILE");
+    if (path && *path) tune_load(path);
+  }
+  for (int i = 0; i < g_tune_count; ++i) {
+    const TuneRow& r = g_tune[i];
+    if (r.dtype == dtype && r.ta == g.transA && r.tb == g.transB && r.m == g.m && r.n == g.n && r.k == g.k)
+      return r.kernel;
+  }
+  return -1;
+}
+
 // ------------------------------------------------------------------ selection --------
 static int select_f32(const GemmArgs& g) {
   if (g.k == 0) return 0;
+  const int tuned = tune_lookup(MMBO_DTYPE_F32, g);
+  if (tuned >= 0) return tuned;
   // The split-precision tensor-core kernels hold the fp32 tolerance and are several
   // times faster than the FFMA pipe once the three launches they need are amortised.
   // MMBO_F32_EXACT=1 keeps automatic selection on the CUDA-core kernels.
@@ -492,6 +565,8 @@ static int select_f32(const GemmArgs& g) {
 
 static int select_f16(const GemmArgs& g) {
   if (g.k == 0) return 0;
+  const int tuned = tune_lookup(MMBO_DTYPE_F16, g);
+  if (tuned >= 0) return tuned;
   // Operands TMA cannot address are realigned through scratch first; that only pays off
   // once the product dwarfs the copies.
   if (!hgemm_tma_ok(g) && (double)g.m * (double)g.n * (double)g.k < 256.0 * 256.0 * 256.0) return 0;
@@ -804,8 +879,39 @@ int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const do
   int rc = validate(g, reinterpret_cast<const float*>(alpha), reinterpret_cast<const float*>(beta));
   if (rc) return rc;
   if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF64)) return MMBO_ERR_BAD_KERNEL_ID;
-  const int id = kernelId == MMBO_KERNEL_AUTO ? 2 : kernelId;  // the fp64 tensor path
+  int id = kernelId;
+  if (id == MMBO_KERNEL_AUTO) {
+    id = tune_lookup(MMBO_DTYPE_F64, g);
+    if (id < 0) id = 2;  // the fp64 tensor path
+  }
   return run_f64(g, *alpha, *beta, id, static_cast<cudaStream_t>(stream));
+}
+
+int mmbo_gemm_strided_batched(int dtype, int transA, int transB, size_t m, size_t n, size_t k, const void* alpha,
+                              const void* A, size_t lda, size_t strideA, const void* B, size_t ldb, size_t strideB,
+                              const void* beta, void* C, size_t ldc, size_t strideC, size_t batch, int kernelId,
+                              void* stream) {
+  if (dtype != MMBO_DTYPE_F16 && dtype != MMBO_DTYPE_F32 && dtype != MMBO_DTYPE_F64) return MMBO_ERR_BAD_DTYPE;
+  const size_t es = dtype == MMBO_DTYPE_F16 ? 2 : dtype == MMBO_DTYPE_F32 ? 4 : 8;
+  for (size_t b = 0; b < batch; ++b) {
+    const char* a = static_cast<const char*>(A) + (A ? b * strideA * es : 0);
+    const char* bb = static_cast<const char*>(B) + (B ? b * strideB * es : 0);
+    char* c = static_cast<char*>(C) + (C ? b * strideC * es : 0);
+    int rc;
+    if (dtype == MMBO_DTYPE_F16)
+      rc = mmbo_gemm_f16(transA, transB, m, n, k, static_cast<const float*>(alpha), a, lda, bb, ldb,
+                         static_cast<const float*>(beta), c, ldc, kernelId, stream);
+    else if (dtype == MMBO_DTYPE_F32)
+      rc = mmbo_gemm_f32(transA, transB, m, n, k, static_cast<const float*>(alpha), reinterpret_cast<const float*>(a),
+                         lda, reinterpret_cast<const float*>(bb), ldb, static_cast<const float*>(beta),
+                         reinterpret_cast<float*>(c), ldc, kernelId, stream);
+    else
+      rc = mmbo_gemm_f64(transA, transB, m, n, k, static_cast<const double*>(alpha), reinterpret_cast<const double*>(a),
+                         lda, reinterpret_cast<const double*>(bb), ldb, static_cast<const double*>(beta),
+                         reinterpret_cast<double*>(c), ldc, kernelId, stream);
+    if (rc) return rc;
+  }
+  return MMBO_OK;
 }
 
 int mmbo_num_kernels(int dtype) {
@@ -841,7 +947,11 @@ int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, si
   if (rc) return rc;
   if (dtype == MMBO_DTYPE_F32) return select_f32(g);
   if (dtype == MMBO_DTYPE_F16) return select_f16(g);
-  if (dtype == MMBO_DTYPE_F64) return g.k == 0 ? 0 : 2;
+  if (dtype == MMBO_DTYPE_F64) {
+    if (g.k == 0) return 0;
+    const int tuned = tune_lookup(MMBO_DTYPE_F64, g);
+    return tuned >= 0 ? tuned : 2;
+  }
   return MMBO_ERR_BAD_DTYPE;
 }
 
@@ -863,6 +973,7 @@ const char* mmbo_status_string(int status) {
     case MMBO_ERR_DEVICE_FAULT: return "a kernel recorded a bounded-wait time-out";
     case MMBO_ERR_TOO_LARGE: return "problem exceeds launch limits of the chosen kernel";
     case MMBO_ERR_WORKSPACE: return "the workspace lent by the caller is too small for this call";
+    case MMBO_ERR_TUNING_FILE: return "tuning file missing or malformed";
     case MMBO_ERR_NOALLOC_TOO_LARGE:
       return "problem needs more scratch than the library's built-in MMBO_NOALLOC_SCRATCH_BYTES";
   }
@@ -955,6 +1066,21 @@ int mmbo_set_workspace(void* ptr, size_t bytes) {
   w.bytes = ptr ? bytes : 0;
   w.user = ptr != nullptr;
   return MMBO_OK;
+}
+
+int mmbo_tuning_set(int dtype, int transA, int transB, size_t m, size_t n, size_t k, int kernelId) {
+  if ((transA != 0 && transA != 1) || (transB != 0 && transB != 1)) return MMBO_ERR_BAD_TRANS;
+  return tune_set(dtype, transA, transB, m, n, k, kernelId);
+}
+
+int mmbo_tuning_load(const char* path) {
+  if (!path) return MMBO_ERR_NULL_POINTER;
+  return tune_load(path);
+}
+
+void mmbo_tuning_clear(void) {
+  g_tune_count = 0;
+  g_tune_env_done = true;  // an explicit clear also cancels the environment file
 }
 
 int mmbo_selftest_bounded_wait(unsigned long long limit_ns, void* stream) {

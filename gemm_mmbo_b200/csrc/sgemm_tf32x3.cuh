@@ -45,32 +45,44 @@ __device__ __forceinline__ float round_tf32(float x) {
 }
 
 // X holds a logical R x K operand: element (r, l) at X[r + l*ld] when ROW_CONTIG, at
-// X[l + r*ld] otherwise.  hi/lo: R rows of Kpad floats, element (r, l) at [r*Kpad + l].
-// Columns l >= K of the scratch rows are never read by the GEMM (its tensor maps end at K).
+// X[l + r*ld] otherwise.  hi/lo: R rows of Kpad floats, element (r, l) at [r*Kpad + l],
+// Kpad a multiple of 32 and the arrays 16-byte aligned (they are this library's scratch),
+// so every store is a 16-byte store whatever the caller's layout.  Columns l >= K of
+// the scratch rows may receive zeros; the GEMM never reads them (its tensor maps end at
+// K).  One block handles a 64 x 64 tile: 16 coalesced 4-byte loads in flight per thread.
+constexpr int kSplitTile = 64;
 template <bool ROW_CONTIG>
 __global__ void __launch_bounds__(256)
 split_pack_kernel(const float* __restrict__ X, size_t ld, uint32_t R, uint32_t K, uint32_t Kpad,
                   float* __restrict__ hi, float* __restrict__ lo) {
-  __shared__ float tile[32][33];
-  const uint32_t tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
-  const uint32_t l0 = blockIdx.x * 32u, r0 = blockIdx.y * 32u;
+  __shared__ float tile[kSplitTile][kSplitTile + 1];  // [l][r], used by the transposing variant
+  const uint32_t tid = threadIdx.x;
+  const uint32_t l0 = blockIdx.x * kSplitTile, r0 = blockIdx.y * kSplitTile;
   if (ROW_CONTIG) {
 #pragma unroll
-    for (uint32_t i = 0; i < 4; ++i) {
-      const uint32_t l = l0 + ty + 8u * i, r = r0 + tx;
-      tile[ty + 8u * i][tx] = (l < K && r < R) ? X[(size_t)r + (size_t)l * ld] : 0.f;
+    for (uint32_t i = 0; i < 16; ++i) {
+      const uint32_t idx = tid + 256u * i, r = idx % kSplitTile, l = idx / kSplitTile;
+      tile[l][r] = (l0 + l < K && r0 + r < R) ? X[(size_t)(r0 + r) + (size_t)(l0 + l) * ld] : 0.f;
     }
     __syncthreads();
   }
 #pragma unroll
-  for (uint32_t i = 0; i < 4; ++i) {
-    const uint32_t r = r0 + ty + 8u * i, l = l0 + tx;
-    if (r < R && l < K) {
-      const float x = ROW_CONTIG ? tile[tx][ty + 8u * i] : X[(size_t)l + (size_t)r * ld];
-      const float h = round_tf32(x);
-      hi[(size_t)r * Kpad + l] = h;
-      lo[(size_t)r * Kpad + l] = round_tf32(x - h);
+  for (uint32_t j = 0; j < 4; ++j) {
+    const uint32_t idx = tid + 256u * j, l4 = (idx % 16u) * 4u, r = idx / 16u;
+    if (r0 + r >= R || l0 + l4 >= Kpad) continue;
+    float x[4];
+#pragma unroll
+    for (uint32_t e = 0; e < 4; ++e) {
+      if (ROW_CONTIG) x[e] = tile[l4 + e][r];
+      else x[e] = (l0 + l4 + e < K) ? X[(size_t)(l0 + l4 + e) + (size_t)(r0 + r) * ld] : 0.f;
     }
+    float4 h, d;
+    h.x = round_tf32(x[0]); h.y = round_tf32(x[1]); h.z = round_tf32(x[2]); h.w = round_tf32(x[3]);
+    d.x = round_tf32(x[0] - h.x); d.y = round_tf32(x[1] - h.y);
+    d.z = round_tf32(x[2] - h.z); d.w = round_tf32(x[3] - h.w);
+    const size_t off = (size_t)(r0 + r) * Kpad + l0 + l4;
+    *reinterpret_cast<float4*>(hi + off) = h;
+    *reinterpret_cast<float4*>(lo + off) = d;
   }
 }
 

@@ -90,6 +90,20 @@ def _haddr(x):
     return int(x.ctypes.data)  # numpy
 
 
+def gemm_strided_batched(dtype, transA, transB, m, n, k, alpha, A, lda, strideA, B, ldb, strideB, beta, C, ldc,
+                         strideC, batch, kernelId: int = KERNEL_AUTO, stream=None) -> None:
+    """`batch` independent GEMMs whose operands are `stride*` elements apart."""
+    dt = _DTYPES[dtype]
+    scalar = ctypes.c_double if dt == DTYPE_F64 else ctypes.c_float
+    a, b = scalar(alpha), scalar(beta)
+    rc = LIB.mmbo_gemm_strided_batched(dt, int(bool(transA)), int(bool(transB)), m, n, k,
+                                       ctypes.cast(ctypes.byref(a), ctypes.c_void_p), _addr(A), lda, strideA,
+                                       _addr(B), ldb, strideB, ctypes.cast(ctypes.byref(b), ctypes.c_void_p),
+                                       _addr(C), ldc, strideC, batch, kernelId, _stream(stream))
+    if rc != 0:
+        raise MmboError(rc, "mmbo_gemm_strided_batched")
+
+
 def _wrap(dtype, ta, tb):
     def f(m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId=KERNEL_AUTO, stream=None):
         gemm(dtype, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId, stream)
@@ -191,3 +205,20 @@ def set_workspace(buf, nbytes: int = 0) -> None:
     rc = LIB.mmbo_set_workspace(_addr(buf), nbytes)
     if rc != 0:
         raise MmboError(rc, "mmbo_set_workspace")
+
+
+def tuning_set(dtype, transA: bool, transB: bool, m: int, n: int, k: int, kernel_id: int) -> None:
+    """Pin the kernel automatic selection uses for one exact problem."""
+    rc = LIB.mmbo_tuning_set(_DTYPES[dtype], int(bool(transA)), int(bool(transB)), m, n, k, kernel_id)
+    if rc != 0:
+        raise MmboError(rc, "mmbo_tuning_set")
+
+
+def tuning_load(path) -> None:
+    rc = LIB.mmbo_tuning_load(str(path).encode())
+    if rc != 0:
+        raise MmboError(rc, "mmbo_tuning_load")
+
+
+def tuning_clear() -> None:
+    LIB.mmbo_tuning_clear()

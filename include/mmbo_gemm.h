@@ -54,6 +54,7 @@ extern "C" {
 #define MMBO_ERR_DEVICE_FAULT (-13)     /* a kernel recorded a bounded-wait time-out */
 #define MMBO_ERR_TOO_LARGE (-14)
 #define MMBO_ERR_WORKSPACE (-15)        /* lent workspace too small or misaligned */
+#define MMBO_ERR_TUNING_FILE (-17)      /* tuning file missing or malformed */
 #define MMBO_ERR_NOALLOC_TOO_LARGE (-16) /* mmbo_gemm_f32_noalloc: scratch need exceeds the built-in array */
 
 /* SGEMM, fp32 storage and arithmetic.  Replaces dgemm_NT / naive_dgemm
@@ -91,6 +92,16 @@ int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const do
                   const double* A, size_t lda, const double* B, size_t ldb, const double* beta,
                   double* C, size_t ldc, int kernelId, void* stream);
 
+/* Strided-batched GEMM: problem b of `batch` uses A + b*strideA, B + b*strideB,
+ * C + b*strideC (strides in elements).  The reference's Tensile argument block already
+ * carries a batch index and these strides (strideC2K / strideA2K / strideB2K and sizeK,
+ * src/gemm/gemm.h:62-69,88-92) with sizeK fixed to 1.  alpha and beta point to float for
+ * f16/f32 and to double for f64.  The problems are queued one after another on `stream`. */
+int mmbo_gemm_strided_batched(int dtype, int transA, int transB, size_t m, size_t n, size_t k,
+                              const void* alpha, const void* A, size_t lda, size_t strideA,
+                              const void* B, size_t ldb, size_t strideB, const void* beta, void* C,
+                              size_t ldc, size_t strideC, size_t batch, int kernelId, void* stream);
+
 /* Kernel table -- the counterpart of naive_kernels / kernels / *_kernel_parameters in
  * src/gemm/constants.h:4-135.  out[8] = {MT0 (tile along m), MT1 (tile along n), threads,
  * DepthU (k per stage), stages, ctaGroup, wgm, usesTensorCores}. */
@@ -102,6 +113,18 @@ int mmbo_kernel_params(int dtype, int kernelId, int out[8]);
 int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, size_t k,
                        const void* A, size_t lda, const void* B, size_t ldb, const void* C,
                        size_t ldc);
+
+/* Tuning table: exact-size overrides of automatic selection, the counterpart of the
+ * reference's Tensile library logic (src/gemm/ref/vega20_Cijk_Ailk_Bjlk_DB.yaml:929-1177).
+ * A row says "for this dtype, transpose mode and (m, n, k) use this kernel id".
+ * mmbo_tuning_load reads rows from a text file (one row per line:
+ * "<f16|f32|f64> <NN|NT|TN|TT> m n k kernelId", '#' comments); the file named by the
+ * environment variable MMBO_TUNING_FILE is loaded on the first automatic selection.
+ * gemm_mmbo_b200/autotune.py measures every kernel on a list of sizes and writes such a
+ * file (the brute-force sweep of src/gemm/benchmark.cc:92-106, persisted). */
+int mmbo_tuning_set(int dtype, int transA, int transB, size_t m, size_t n, size_t k, int kernelId);
+int mmbo_tuning_load(const char* path);
+void mmbo_tuning_clear(void);
 
 const char* mmbo_status_string(int status);
 

