@@ -429,6 +429,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!mbar_wait(cload_bar(epi_w, b), cphase[b], abort_flag, kFaultWaitCLoad, epi_w)) ok = false;
           cphase[b] ^= 1u;
         }
+        if (tracer && c == 0) trace_stamp(p.trace, local_tile, 4);  // old C of chunk 0 has arrived
         // `ok` may differ between lanes only after a time-out, when the data is
         // discarded anyway; keep the warp converged for the aligned tcgen05 ops.
         if constexpr (!kEarlyDrain) {
@@ -463,9 +464,11 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             *reinterpret_cast<uint4*>(addr) = out;
           }
         }
+        if (tracer && c == 0) trace_stamp(p.trace, local_tile, 11);  // chunk 0 written to staging
         if (c_tma) {
           fence_proxy_async_smem();
           __syncwarp();
+          if (tracer && c == 0) trace_stamp(p.trace, local_tile, 12);  // fenced
           if (lane == 0) {
             if (in_range && ok && (p.diag & 1u) == 0u)
               tma_store_2d(&tmap_c, sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));

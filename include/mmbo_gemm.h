@@ -202,7 +202,7 @@ int mmbo_selftest_bounded_wait(unsigned long long limit_ns, void* stream);
  * a device buffer; the following HGEMM launches record clock stamps of CTA 0 for their
  * first 64 tiles (16 words per tile: 0 tile start, 1 C requests issued, 2 accumulator
  * ready, 3 accumulator released, 4 old C arrived, 5/6 chunk stored, 8 issuer starts waiting
- * for a free accumulator, 9 got it, 10 all UMMAs issued).  mmbo_debug_trace(0, out, words)
+ * for a free accumulator, 9 got it, 10 all UMMAs issued, 11 chunk 0 in staging, 12 fenced).  mmbo_debug_trace(0, out, words)
  * copies the buffer to host memory and disarms. */
 int mmbo_debug_trace(int enable, unsigned long long* out, size_t words);
 
