@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+
+#include <mutex>
 #include <stdlib.h>
 #include <string.h>
 
@@ -71,6 +73,13 @@ static const KernelRow* rows_of(int dtype, int* count) {
   *count = 0;
   return nullptr;
 }
+
+// One lock for the library's host-side state (per-device caches of attributes, scratch
+// buffers, staging pipes, the tuning table, the trace buffer).  Entry points that launch
+// take it for the duration of the call, so concurrent callers are serialised on the host
+// only; the work they queue still overlaps on the GPU.
+static std::recursive_mutex g_api_mutex;
+#define MMBO_API_LOCK() std::lock_guard<std::recursive_mutex> mmbo_api_lock_(g_api_mutex)
 
 // ------------------------------------------------------------------ device info ------
 constexpr int kMaxDevices = 64;
@@ -825,6 +834,7 @@ extern "C" {
 int mmbo_gemm_f32(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
                   const float* A, size_t lda, const float* B, size_t ldb, const float* beta, float* C,
                   size_t ldc, int kernelId, void* stream) {
+  MMBO_API_LOCK();
   GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
   int rc = validate(g, alpha, beta);
   if (rc) return rc;
@@ -838,6 +848,7 @@ int mmbo_gemm_f32(int transA, int transB, size_t m, size_t n, size_t k, const fl
 int mmbo_gemm_f16(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha, const void* A,
                   size_t lda, const void* B, size_t ldb, const float* beta, void* C, size_t ldc,
                   int kernelId, void* stream) {
+  MMBO_API_LOCK();
   GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
   int rc = validate(g, alpha, beta);
   if (rc) return rc;
@@ -851,6 +862,7 @@ int mmbo_gemm_f16(int transA, int transB, size_t m, size_t n, size_t k, const fl
 int mmbo_gemm_f32_host(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha, const float* A,
                        size_t lda, const float* B, size_t ldb, const float* beta, float* C, size_t ldc,
                        int kernelId) {
+  MMBO_API_LOCK();
   GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
   int rc = validate(g, alpha, beta);
   if (rc) return rc;
@@ -863,6 +875,7 @@ int mmbo_gemm_f32_host(int transA, int transB, size_t m, size_t n, size_t k, con
 int mmbo_gemm_f16_host(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha, const void* A,
                        size_t lda, const void* B, size_t ldb, const float* beta, void* C, size_t ldc,
                        int kernelId) {
+  MMBO_API_LOCK();
   GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
   int rc = validate(g, alpha, beta);
   if (rc) return rc;
@@ -875,6 +888,7 @@ int mmbo_gemm_f16_host(int transA, int transB, size_t m, size_t n, size_t k, con
 int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const double* alpha, const double* A,
                   size_t lda, const double* B, size_t ldb, const double* beta, double* C, size_t ldc,
                   int kernelId, void* stream) {
+  MMBO_API_LOCK();
   GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
   int rc = validate(g, reinterpret_cast<const float*>(alpha), reinterpret_cast<const float*>(beta));
   if (rc) return rc;
@@ -941,6 +955,7 @@ int mmbo_kernel_params(int dtype, int kernelId, int out[8]) {
 
 int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, size_t k, const void* A,
                        size_t lda, const void* B, size_t ldb, const void* C, size_t ldc) {
+  MMBO_API_LOCK();
   GemmArgs g{transA, transB, m, n, k, A, B, const_cast<void*>(C), lda, ldb, ldc, 1.f, 0.f};
   const float one = 1.f;
   int rc = validate(g, &one, &one);
@@ -1004,6 +1019,7 @@ int mmbo_shard_columns(size_t n, int nGpus, int rank, size_t align, size_t* col0
 
 static int fill_common(int dtype, void* dst, size_t rows, size_t cols, size_t ld, uint64_t seed, uint32_t mat,
                        int dist, float scale, size_t row0, size_t col0, size_t total_rows, void* stream) {
+  MMBO_API_LOCK();
   if (rows == 0 || cols == 0) return MMBO_OK;
   if (!dst) return MMBO_ERR_NULL_POINTER;
   if (ld < rows) return MMBO_ERR_BAD_LDC;
@@ -1040,6 +1056,7 @@ int mmbo_fill_f16(void* dst, size_t rows, size_t cols, size_t ld, uint64_t seed,
 }
 
 int mmbo_gemm_workspace_bytes(int dtype, int kernelId, size_t m, size_t n, size_t k, size_t* bytes) {
+  MMBO_API_LOCK();
   if (!bytes) return MMBO_ERR_NULL_POINTER;
   int count = 0;
   if (!rows_of(dtype, &count)) return MMBO_ERR_BAD_DTYPE;
@@ -1054,6 +1071,7 @@ int mmbo_gemm_workspace_bytes(int dtype, int kernelId, size_t m, size_t n, size_
 }
 
 int mmbo_set_workspace(void* ptr, size_t bytes) {
+  MMBO_API_LOCK();
   const int dev = current_device();
   if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
   Workspace& w = g_ws[dev];
@@ -1069,16 +1087,19 @@ int mmbo_set_workspace(void* ptr, size_t bytes) {
 }
 
 int mmbo_tuning_set(int dtype, int transA, int transB, size_t m, size_t n, size_t k, int kernelId) {
+  MMBO_API_LOCK();
   if ((transA != 0 && transA != 1) || (transB != 0 && transB != 1)) return MMBO_ERR_BAD_TRANS;
   return tune_set(dtype, transA, transB, m, n, k, kernelId);
 }
 
 int mmbo_tuning_load(const char* path) {
+  MMBO_API_LOCK();
   if (!path) return MMBO_ERR_NULL_POINTER;
   return tune_load(path);
 }
 
 void mmbo_tuning_clear(void) {
+  MMBO_API_LOCK();
   g_tune_count = 0;
   g_tune_env_done = true;  // an explicit clear also cancels the environment file
 }
@@ -1090,6 +1111,7 @@ int mmbo_selftest_bounded_wait(unsigned long long limit_ns, void* stream) {
 }
 
 int mmbo_debug_trace(int enable, unsigned long long* out, size_t words) {
+  MMBO_API_LOCK();
   // enable != 0: allocate and clear the trace buffer, later launches record into it;
   // enable == 0: copy up to `words` words to `out` (host) and disarm.
   if (enable) {
@@ -1108,6 +1130,7 @@ int mmbo_debug_trace(int enable, unsigned long long* out, size_t words) {
 }
 
 int mmbo_device_status(unsigned int* status) {
+  MMBO_API_LOCK();
   if (!status) return MMBO_ERR_NULL_POINTER;
   unsigned int v = 0;
   cudaError_t e = cudaDeviceSynchronize();
@@ -1134,6 +1157,7 @@ static void* g_noalloc_scratch_addr[kMaxDevices];
 int mmbo_gemm_f32_noalloc(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
                           const float* A, size_t lda, const float* B, size_t ldb, const float* beta, float* C,
                           size_t ldc, void* stream) {
+  MMBO_API_LOCK();
   GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
   int rc = validate(g, alpha, beta);
   if (rc) return rc;
