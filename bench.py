@@ -136,13 +136,13 @@ def cpu_panel_time(O, w, pm: int, pn: int, repeats: int = 1) -> float:
     return best
 
 
-def cpu_baseline(w, budget_s: float = 12.0):
+def cpu_baseline(w, target_s: float = 12.0):
     from oracle import oracle as O
     O.set_num_threads(0)  # every host core, even when the launcher exported OMP_NUM_THREADS=1
     t = cpu_panel_time(O, w, 512, 512)
     rate = 2.0 * 512 * 512 * w["k"] / t  # flop/s
-    # panel edge for ~budget_s of work, multiple of 256, within the problem
-    edge = int((rate * budget_s / (2.0 * w["k"])) ** 0.5) // 256 * 256
+    # panel edge for ~target_s of work, multiple of 256, within the problem
+    edge = int((rate * target_s / (2.0 * w["k"])) ** 0.5) // 256 * 256
     edge = max(512, min(edge, w["m"], w["n"], 8192))
     t = cpu_panel_time(O, w, edge, edge)
     tflops = 2.0 * edge * edge * w["k"] / t / 1e12

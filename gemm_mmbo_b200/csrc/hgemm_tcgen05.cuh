@@ -344,7 +344,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (nm0 + 64u * c < p.m && nn0 < p.n)
             tma_prefetch_l2_2d(&tmap_c, static_cast<int32_t>(nm0 + 64u * c), static_cast<int32_t>(nn0));
       }
-      // Every lane polls; the verdict is made warp-uniform so that the aligned
+      // Every lane polls; the outcome is made warp-uniform so that the aligned
       // tcgen05 instructions below always run with a converged warp.
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag,
                                              kFaultWaitTmemFull, acc));

@@ -33,7 +33,7 @@ def build(force: bool = False) -> pathlib.Path:
     return _LIB_PATH
 
 
-def build_ref(reference_root: str = "/root/reference") -> pathlib.Path | None:
+def build_ref(reference_root: str) -> pathlib.Path | None:
     """Compile the reference's own remap checker into oracle/_ref/ if its source exists."""
     src = pathlib.Path(reference_root) / "src/gemm/ref/map.cpp"
     if not src.exists():

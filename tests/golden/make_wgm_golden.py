@@ -7,7 +7,7 @@ Output: a compressed array file holding the four integer columns in file order a
         SHA-256 of the text it was parsed from.
 
 Run once where the reference tree is mounted:
-    python tests/golden/make_wgm_golden.py /root/reference
+    python tests/golden/make_wgm_golden.py <root of the reference tree>
 """
 import hashlib
 import pathlib
@@ -18,7 +18,9 @@ import numpy as np
 
 
 def main() -> None:
-    ref_root = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    ref_root = pathlib.Path(sys.argv[1])
     text = (ref_root / "src/gemm/ref/res").read_bytes()
     pat = re.compile(rb"\((\d+),(\d+)\)--->\s*\((\d+),\s*(\d+)\) in original map")
     rows = [tuple(int(g) for g in m.groups()) for m in pat.finditer(text)]
