@@ -79,3 +79,50 @@ def test_unequal_blocks_refuse_gather():
     sh = ColumnShard(1000, 3, 0, align=128)
     with pytest.raises(ValueError):
         sh.gather(torch.zeros((sh.ncols, 8)), torch.zeros((1000, 8)), 8)
+
+
+def _absent_peer_worker(rank: int, world: int, port: int, q):
+    """Rank 1 never enters the exchange; rank 0 must get an error after the group's
+    time-out instead of waiting forever (failure made on the host, no GPU involved)."""
+    import datetime
+    import time
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        from gemm_mmbo_b200.sharded import ColumnShard
+        sh = ColumnShard(256, world, rank, align=64)
+        if rank == 1:
+            time.sleep(12)  # absent from the collective
+            q.put((rank, "absent"))
+            return
+        mine = torch.zeros((sh.ncols, 8), dtype=torch.float16)
+        out = torch.zeros((256, 8), dtype=torch.float16)
+        t0 = time.time()
+        try:
+            sh.gather(mine, out, 8)
+            q.put((rank, "no error"))
+        except Exception as e:  # gloo reports the time-out as a RuntimeError
+            q.put((rank, f"error after {time.time() - t0:.0f}s: {type(e).__name__}"))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+@pytest.mark.timeout(120)
+def test_gather_reports_an_absent_rank_instead_of_hanging():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_absent_peer_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=90) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+        if p.is_alive():
+            p.kill()
+    assert results[1] == "absent"
+    assert results[0].startswith("error after"), results
