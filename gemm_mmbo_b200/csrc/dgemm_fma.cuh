@@ -21,6 +21,7 @@ struct DgemmParams {
   uint32_t lda, ldb, ldc;
   double alpha, beta;
   uint32_t wgm;
+  uint32_t diag;  // diagnostic runs only (bit 0: no C traffic; results wrong by design), never set in production
 };
 
 constexpr int kDgBM = 64, kDgBN = 64, kDgBK = 16, kDgThreads = 256;

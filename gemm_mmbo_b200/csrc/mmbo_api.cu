@@ -15,6 +15,7 @@
 
 #include "../../include/mmbo_gemm.h"
 #include "dgemm_dmma.cuh"
+#include "dgemm_dmma_ws.cuh"
 #include "dgemm_fma.cuh"
 #include "hgemm_tcgen05.cuh"
 #include "ref_kernels.cuh"
@@ -52,6 +53,7 @@ static const KernelRow kF64Rows[] = {
     {"dgemm_simple_MT032x008x01_TT01_01_WG256", 32, 8, 256, 1, 1, 1, 1, 0},
     {"dgemm_fma_MT064x064x16_TT04_04_WG256_WGM08", 64, 64, 256, 16, 2, 1, 8, 0},
     {"dgemm_dmma_MT128x064x08_WT32_32_WG256_WGM08", 128, 64, 256, 8, 2, 1, 8, 1},
+    {"dgemm_dmma_ws_MT128x064x16_S4_WT64_32_WG160_WGM08", 128, 64, 160, 16, 4, 1, 8, 1},
 };
 constexpr int kNumF64 = sizeof(kF64Rows) / sizeof(KernelRow);
 constexpr int kNumF32 = sizeof(kF32Rows) / sizeof(KernelRow);
@@ -634,11 +636,12 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
     else gemm_simple_f64_kernel<<<grid, block, 0, st>>>(g.transA, g.transB, g.m, g.n, g.k, alpha, A, g.lda, B, g.ldb, beta, C, g.ldc);
     return (int)cudaGetLastError();
   }
-  if (id != 1 && id != 2) return MMBO_ERR_BAD_KERNEL_ID;
+  if (id < 1 || id > 3) return MMBO_ERR_BAD_KERNEL_ID;
   DgemmParams p;
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
   p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
   p.alpha = alpha; p.beta = beta; p.wgm = env_u32("MMBO_WGM", kF64Rows[id].wgm);
+  p.diag = env_u32("MMBO_DIAG", 0);
   if (id == 2) {  // fp64 tensor path
     const size_t gx2 = (g.m + kDmBM - 1) / kDmBM, gy2 = (g.n + kDmBN - 1) / kDmBN;
     if (gy2 > 65535) return MMBO_ERR_TOO_LARGE;
@@ -648,6 +651,21 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
     else if (g.transA && !g.transB) dgemm_dmma_kernel<true, false><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
     else dgemm_dmma_kernel<true, true><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
     return (int)cudaGetLastError();
+  }
+  if (id == 3) {  // fp64 tensor path, producer warp + consumer warps, persistent
+    const size_t tiles = ((g.m + kWsBM - 1) / kWsBM) * ((g.n + kWsBN - 1) / kWsBN);
+    if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
+    const unsigned grid3 = (unsigned)std::min(tiles, (size_t)2 * (size_t)sm_count());  // two CTAs per SM
+    auto launch = [&](auto kernel) -> int {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWsSmemBytes);
+      if (e != cudaSuccess) return (int)e;
+      kernel<<<grid3, kWsThreads, kWsSmemBytes, st>>>(A, B, C, p);
+      return (int)cudaGetLastError();
+    };
+    if (!g.transA && !g.transB) return launch(dgemm_dmma_ws_kernel<false, false>);
+    if (!g.transA && g.transB) return launch(dgemm_dmma_ws_kernel<false, true>);
+    if (g.transA && !g.transB) return launch(dgemm_dmma_ws_kernel<true, false>);
+    return launch(dgemm_dmma_ws_kernel<true, true>);
   }
   const size_t gx = (g.m + kDgBM - 1) / kDgBM, gy = (g.n + kDgBN - 1) / kDgBN;
   if (gy > 65535) return MMBO_ERR_TOO_LARGE;
@@ -896,7 +914,7 @@ int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const do
   int id = kernelId;
   if (id == MMBO_KERNEL_AUTO) {
     id = tune_lookup(MMBO_DTYPE_F64, g);
-    if (id < 0) id = 2;  // the fp64 tensor path
+    if (id < 0) id = 3;  // the fp64 tensor path, warp-specialised
   }
   return run_f64(g, *alpha, *beta, id, static_cast<cudaStream_t>(stream));
 }
@@ -965,7 +983,7 @@ int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, si
   if (dtype == MMBO_DTYPE_F64) {
     if (g.k == 0) return 0;
     const int tuned = tune_lookup(MMBO_DTYPE_F64, g);
-    return tuned >= 0 ? tuned : 2;
+    return tuned >= 0 ? tuned : 3;
   }
   return MMBO_ERR_BAD_DTYPE;
 }
