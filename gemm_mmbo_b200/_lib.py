@@ -32,6 +32,8 @@ SIGNATURES = {
                                           _fp, _vp, _sz, ctypes.c_int]),
     "mmbo_gemm_f16_host": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
                                           _fp, _vp, _sz, ctypes.c_int]),
+    "mmbo_gemm_f64_host": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _dp, _vp, _sz, _vp, _sz,
+                                          _dp, _vp, _sz, ctypes.c_int]),
     "mmbo_gemm_strided_batched": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _vp, _vp,
                                                  _sz, _sz, _vp, _sz, _sz, _vp, _vp, _sz, _sz, _sz, ctypes.c_int, _vp]),
     "mmbo_num_kernels": (ctypes.c_int, [ctypes.c_int]),

@@ -765,8 +765,8 @@ static int pipe_setup(HostPipe& hp, size_t bytes) {
   return MMBO_OK;
 }
 
-static int gemm_host(int dtype, const GemmArgs& h, int kernelId) {
-  const size_t es = dtype == MMBO_DTYPE_F32 ? 4 : 2;
+static int gemm_host(int dtype, const GemmArgs& h, int kernelId, double alpha64 = 0.0, double beta64 = 0.0) {
+  const size_t es = dtype == MMBO_DTYPE_F64 ? 8 : dtype == MMBO_DTYPE_F32 ? 4 : 2;
   const int dev = current_device();
   if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
   if (h.m == 0 || h.n == 0) return MMBO_OK;
@@ -790,7 +790,7 @@ static int gemm_host(int dtype, const GemmArgs& h, int kernelId) {
   char* dA = static_cast<char*>(hp.buf);
   char* dB[2] = {dA + a_bytes, dA + a_bytes + b_bytes};
   char* dC[2] = {dA + a_bytes + 2 * b_bytes, dA + a_bytes + 2 * b_bytes + c_bytes};
-  const bool use_c = h.beta != 0.f;
+  const bool use_c = dtype == MMBO_DTYPE_F64 ? beta64 != 0.0 : h.beta != 0.f;
   cudaError_t e;
   if (h.k > 0) {
     e = cudaMemcpy2DAsync(dA, dlda * es, h.A, h.lda * es, rowsA * es, colsA, cudaMemcpyHostToDevice, hp.s_in);
@@ -822,7 +822,13 @@ static int gemm_host(int dtype, const GemmArgs& h, int kernelId) {
     GemmArgs g = h;
     g.n = w; g.A = dA; g.lda = dlda; g.B = dB[b]; g.ldb = dldb; g.C = dC[b]; g.ldc = dldc;
     int id = kernelId;
-    if (dtype == MMBO_DTYPE_F32) {
+    if (dtype == MMBO_DTYPE_F64) {
+      if (id == MMBO_KERNEL_AUTO) {
+        id = tune_lookup(MMBO_DTYPE_F64, g);
+        if (id < 0) id = 3;
+      }
+      rc = run_f64(g, alpha64, beta64, id, hp.s_mm);
+    } else if (dtype == MMBO_DTYPE_F32) {
       if (id == MMBO_KERNEL_AUTO) id = select_f32(g);
       rc = run_f32(g, id, hp.s_mm);
     } else {
@@ -917,6 +923,17 @@ int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const do
     if (id < 0) id = 3;  // the fp64 tensor path, warp-specialised
   }
   return run_f64(g, *alpha, *beta, id, static_cast<cudaStream_t>(stream));
+}
+
+int mmbo_gemm_f64_host(int transA, int transB, size_t m, size_t n, size_t k, const double* alpha, const double* A,
+                       size_t lda, const double* B, size_t ldb, const double* beta, double* C, size_t ldc,
+                       int kernelId) {
+  MMBO_API_LOCK();
+  GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
+  int rc = validate(g, reinterpret_cast<const float*>(alpha), reinterpret_cast<const float*>(beta));
+  if (rc) return rc;
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF64)) return MMBO_ERR_BAD_KERNEL_ID;
+  return gemm_host(MMBO_DTYPE_F64, g, kernelId, *alpha, *beta);
 }
 
 int mmbo_gemm_strided_batched(int dtype, int transA, int transB, size_t m, size_t n, size_t k, const void* alpha,

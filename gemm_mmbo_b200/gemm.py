@@ -74,8 +74,9 @@ def gemm_host(dtype, transA: bool, transB: bool, m: int, n: int, k: int, alpha: 
     """Same GEMM with A, B, C in host memory (pinned torch tensors, numpy arrays or raw
     addresses); returns when C holds the result."""
     dt = _DTYPES[dtype]
-    name = {DTYPE_F32: "mmbo_gemm_f32_host", DTYPE_F16: "mmbo_gemm_f16_host"}[dt]
-    a, b = ctypes.c_float(alpha), ctypes.c_float(beta)
+    name = {DTYPE_F32: "mmbo_gemm_f32_host", DTYPE_F16: "mmbo_gemm_f16_host", DTYPE_F64: "mmbo_gemm_f64_host"}[dt]
+    scalar = ctypes.c_double if dt == DTYPE_F64 else ctypes.c_float
+    a, b = scalar(alpha), scalar(beta)
     rc = getattr(LIB, name)(int(bool(transA)), int(bool(transB)), m, n, k, ctypes.byref(a), _haddr(A), lda,
                             _haddr(B), ldb, ctypes.byref(b), _haddr(C), ldc, kernelId)
     if rc != 0:

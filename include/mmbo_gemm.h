@@ -91,6 +91,12 @@ int mmbo_gemm_f16_host(int transA, int transB, size_t m, size_t n, size_t k, con
 int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const double* alpha,
                   const double* A, size_t lda, const double* B, size_t ldb, const double* beta,
                   double* C, size_t ldc, int kernelId, void* stream);
+/* The same with A, B and C in host memory, as mmbo_gemm_f32_host: the whole of what the
+ * reference's benchmark does around dgemm_NT (hipMalloc, hipMemcpy in, launch, hipMemcpy
+ * out: src/gemm/benchmark.cc:57-63,72-88) in one call. */
+int mmbo_gemm_f64_host(int transA, int transB, size_t m, size_t n, size_t k, const double* alpha,
+                       const double* A, size_t lda, const double* B, size_t ldb, const double* beta,
+                       double* C, size_t ldc, int kernelId);
 
 /* Strided-batched GEMM: problem b of `batch` uses A + b*strideA, B + b*strideB,
  * C + b*strideC (strides in elements).  The reference's Tensile argument block already

@@ -1,4 +1,4 @@
-"""GEMM on host-resident operands (mmbo_gemm_f16_host / mmbo_gemm_f32_host): the library
+"""GEMM on host-resident operands (mmbo_gemm_f16_host / mmbo_gemm_f32_host / mmbo_gemm_f64_host): the library
 stages A once and pipelines column panels of B and C; results must equal the oracle's
 within the dtype's tolerance and host padding rows must stay untouched."""
 import numpy as np
@@ -9,7 +9,7 @@ from helpers import Case, TOL, bits
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("dtype", ["f16", "f32"])
+@pytest.mark.parametrize("dtype", ["f16", "f32", "f64"])
 @pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
 def test_host_operands_match_oracle(cuda, mm, oracle, dtype, ta, tb):
     # n spans several 256-column panels (ragged last one); m and k ragged as well
