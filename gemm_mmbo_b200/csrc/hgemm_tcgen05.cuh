@@ -38,6 +38,8 @@
 
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "ptx.cuh"
 #include "raster.h"
 
@@ -61,10 +63,15 @@ struct HgemmSmem {
   static constexpr int kAopBytes = kAopRows * kBlockK * 2;  // op(A) tile  (UMMA B operand)
   static constexpr int kStageBytes = kBopBytes + kAopBytes;
   static constexpr int kEpiOffset = STAGES * kStageBytes;
-  static constexpr int kEpiBytes = EW * 2 * kEpiBufBytes;
+  // Staging buffers per epilogue warp: two; with 8 epilogue warps (at most two chunks per warp
+  // and tile) two sets of two, so that the old C of the next tile can be requested a whole
+  // tile ahead while this tile's set is still in use.
+  static constexpr int kCSets = EW == 8 ? 2 : 1;
+  static constexpr int kBufsPerWarp = 2 * kCSets;
+  static constexpr int kEpiBytes = EW * kBufsPerWarp * kEpiBufBytes;
   static constexpr int kBarOffset = kEpiOffset + kEpiBytes;
-  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], cload[EW][2]
-  static constexpr int kNumBars = 2 * STAGES + 4 + 2 * EW;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], cload[EW][kBufsPerWarp]
+  static constexpr int kNumBars = 2 * STAGES + 4 + kBufsPerWarp * EW;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
   static constexpr int kTotal = kMiscOffset + 16;
   static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024 bytes
@@ -132,7 +139,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
   auto tmem_full_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tmem_empty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
-  auto cload_bar = [&](uint32_t w, uint32_t b) { return bar_base + 8u * (2 * STAGES + 4 + 2 * w + b); };
+  auto cload_bar = [&](uint32_t w, uint32_t b) { return bar_base + 8u * (2 * STAGES + 4 + L::kBufsPerWarp * w + b); };
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOffset);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOffset + 4);
 
@@ -153,7 +160,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(tmem_empty_bar(a), EW * CG);
     }
     for (uint32_t w = 0; w < EW; ++w)
-      for (uint32_t b = 0; b < 2; ++b) mbar_init(cload_bar(w, b), 1);
+      for (uint32_t b = 0; b < (uint32_t)L::kBufsPerWarp; ++b) mbar_init(cload_bar(w, b), 1);
     fence_mbar_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
@@ -296,14 +303,40 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t q = warp & 3u;
     const uint32_t epi_w = warp - 2u;
     const uint32_t col_base = (epi_w >> 2) * kChunksPerWarp * 64u;  // first accumulator column of this warp
-    const uint32_t buf_base = smem_base + L::kEpiOffset + epi_w * 2u * kEpiBufBytes;
-    uint8_t* buf_gen = smem_gen + L::kEpiOffset + epi_w * 2u * kEpiBufBytes;
+    const uint32_t warp_buf_base = smem_base + L::kEpiOffset + epi_w * L::kBufsPerWarp * kEpiBufBytes;
+    uint8_t* warp_buf_gen = smem_gen + L::kEpiOffset + epi_w * L::kBufsPerWarp * kEpiBufBytes;
     const bool use_c = (p.beta != 0.0f);
     const bool c_tma = p.c_tma != 0u;
     const float alpha = p.alpha, beta = p.beta;
+    const uint64_t alpha2 = pack_f32x2(__float_as_uint(alpha), __float_as_uint(alpha));
+    const uint64_t beta2 = pack_f32x2(__float_as_uint(beta), __float_as_uint(beta));
+    const bool alpha_one = alpha == 1.0f;
     uint32_t local_tile = 0;
-    uint32_t cphase[2] = {0u, 0u};
+    uint32_t cphase = 0;  // bit b: phase parity of the load barrier of buffer b
     bool ok = true;
+    // With two buffer sets the old C of tile i + 1 is requested at the start of tile i (into
+    // the set tile i - 1 used), so that its HBM latency hides behind a whole tile.
+    constexpr bool kCAhead = L::kCSets == 2;
+    static_assert(!kCAhead || kChunksPerWarp <= 2, "C one tile ahead needs a buffer per chunk");
+    uint32_t c_in_flight = 0;  // bit b: a load into buffer b of this warp has been requested and not yet awaited
+    auto request_c = [&](uint32_t t, uint32_t set) {  // whole warp; lane 0 issues: chunks of tile t into buffer set `set`
+      uint32_t tm, tn;
+      mmbo_tile_from_serial(t, p.tiles_m, p.tiles_n, p.wgm, &tm, &tn);
+      const uint32_t mr = tm * TM + col_base, nc = (tn * CG + cta_rank) * kTileN + 32u * q;
+#pragma unroll
+      for (uint32_t c = 0; c < (kChunksPerWarp < 2u ? kChunksPerWarp : 2u); ++c) {
+        const uint32_t mrow0 = mr + 64u * c;
+        if (mrow0 < p.m && nc < p.n) {
+          c_in_flight |= 1u << (2u * set + c);
+          if (lane == 0) {
+            mbar_expect_tx(cload_bar(epi_w, 2u * set + c), kEpiBufBytes);
+            tma_load_2d(warp_buf_base + (2u * set + c) * kEpiBufBytes, &tmap_c, cload_bar(epi_w, 2u * set + c),
+                        static_cast<int32_t>(mrow0), static_cast<int32_t>(nc));
+          }
+        }
+      }
+    };
+    if (kCAhead && p.c_tma != 0u && use_c && walker < num_tiles) request_c(walker, 0u);
     for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers, ++local_tile) {
       uint32_t tm_idx, tn_idx;
       mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
@@ -317,25 +350,19 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // for the accumulator, so that its latency overlaps the main loop of this tile.
       const bool tracer = (warp == 2u && lane == 0u);
       if (tracer) trace_stamp(p.trace, local_tile, 0);
-      if (c_tma && use_c) {
-        if (lane == 0) tma_store_wait_read<0>();  // both buffers' stores have read them
+      // buffer set of this tile (always 0 unless C is requested one tile ahead)
+      const uint32_t set = (kCAhead && c_tma && use_c) ? (local_tile & 1u) : 0u;
+      const uint32_t buf_base = warp_buf_base + 2u * set * kEpiBufBytes;
+      uint8_t* buf_gen = warp_buf_gen + 2u * set * kEpiBufBytes;
+      if (!kCAhead && c_tma && use_c) {
+        if (lane == 0) tma_store_wait_read<0>();  // the previous tile's stores have read their buffers
         __syncwarp();
-        if (lane == 0) {
-#pragma unroll
-          for (uint32_t c = 0; c < (kChunksPerWarp < 2u ? kChunksPerWarp : 2u); ++c) {
-            const uint32_t mrow0 = m0 + 64u * c;
-            if (mrow0 < p.m && ncol0 < p.n) {
-              mbar_expect_tx(cload_bar(epi_w, c), kEpiBufBytes);
-              tma_load_2d(buf_base + c * kEpiBufBytes, &tmap_c, cload_bar(epi_w, c),
-                          static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
-            }
-          }
-        }
+        request_c(tile, 0u);
       }
       if (tracer) trace_stamp(p.trace, local_tile, 1);
       // ... and the old C of the tile after this one is pulled into L2 now, one whole tile
       // ahead, so that those requests will not have to go to HBM.
-      if (c_tma && use_c && lane == 0 && tile + num_walkers < num_tiles) {
+      if (!kCAhead && c_tma && use_c && lane == 0 && tile + num_walkers < num_tiles) {
         uint32_t nm, nn;
         mmbo_tile_from_serial(tile + num_walkers, p.tiles_m, p.tiles_n, p.wgm, &nm, &nn);
         const uint32_t nm0 = nm * TM + col_base, nn0 = (nn * CG + cta_rank) * kTileN + 32u * q;
@@ -365,7 +392,18 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // registers first and the accumulator handed back at once: for short contractions
       // the time an accumulator stays occupied bounds the kernel.
       constexpr bool kEarlyDrain = kChunksPerWarp <= 2;
-      uint32_t racc[kEarlyDrain ? 2 * kChunksPerWarp : 2][32];
+      // Otherwise two register buffers of one chunk each: the tensor-memory loads of chunk
+      // c + 1 are in flight while chunk c is scaled, converted and staged.
+      uint32_t racc[kEarlyDrain ? 2 * kChunksPerWarp : 4][32];
+      auto load_chunk = [&](const uint32_t c, uint32_t (&lo)[32], uint32_t (&hi)[32]) {
+        if (drain) {
+          tmem_ld_32x32(t_warp + 64u * c, lo);
+          tmem_ld_32x32(t_warp + 64u * c + 32u, hi);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) lo[e] = hi[e] = 0u;
+        }
+      };
       if constexpr (kEarlyDrain) {
 #pragma unroll
         for (uint32_t i = 0; i < 2 * kChunksPerWarp; ++i) {
@@ -378,8 +416,17 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tmem_ld_wait();
         release_accumulator();
         if (tracer) trace_stamp(p.trace, local_tile, 3);
+        if (kCAhead && c_tma && use_c && tile + num_walkers < num_tiles) {
+          // The other buffer set was last read by the previous tile's stores, issued a drain
+          // ago: by now they have long left shared memory, so this wait does not stall.
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+          request_c(tile + num_walkers, set ^ 1u);
+        }
       }
-      auto do_chunk = [&](const uint32_t c) {
+      if constexpr (!kEarlyDrain) load_chunk(0u, racc[0], racc[1]);
+      auto do_chunk = [&](const uint32_t c, auto parity) {
+        constexpr uint32_t kPb = decltype(parity)::value;  // register buffer of this chunk (non-early drain)
         const uint32_t b = c & 1u;
         const uint32_t sbuf = buf_base + b * kEpiBufBytes;
         uint8_t* gbuf = buf_gen + b * kEpiBufBytes;
@@ -391,9 +438,10 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // The store issued from this buffer two chunks ago must have read it.
             if (lane == 0) tma_store_wait_read<1>();
             __syncwarp();
+            if (load_c) c_in_flight |= 1u << (2u * set + b);
             if (load_c && lane == 0) {  // chunks beyond the two requested up front
-              mbar_expect_tx(cload_bar(epi_w, b), kEpiBufBytes);
-              tma_load_2d(sbuf, &tmap_c, cload_bar(epi_w, b), static_cast<int32_t>(mrow0),
+              mbar_expect_tx(cload_bar(epi_w, 2u * set + b), kEpiBufBytes);
+              tma_load_2d(sbuf, &tmap_c, cload_bar(epi_w, 2u * set + b), static_cast<int32_t>(mrow0),
                           static_cast<int32_t>(ncol0));
             }
           }
@@ -416,51 +464,42 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             __syncwarp();
           }
         }
-        if constexpr (!kEarlyDrain) {
-          if (drain) {
-            tmem_ld_32x32(t_warp + 64u * c, racc[0]);
-            tmem_ld_32x32(t_warp + 64u * c + 32u, racc[1]);
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) racc[0][e] = racc[1][e] = 0u;
-          }
-        }
         if (c_tma && load_c) {
-          if (!mbar_wait(cload_bar(epi_w, b), cphase[b], abort_flag, kFaultWaitCLoad, epi_w)) ok = false;
-          cphase[b] ^= 1u;
+          if (!mbar_wait(cload_bar(epi_w, 2u * set + b), (cphase >> (2u * set + b)) & 1u, abort_flag, kFaultWaitCLoad,
+                         epi_w))
+            ok = false;
+          cphase ^= 1u << (2u * set + b);
+          c_in_flight &= ~(1u << (2u * set + b));
         }
         if (tracer && c == 0) trace_stamp(p.trace, local_tile, 4);  // old C of chunk 0 has arrived
         // `ok` may differ between lanes only after a time-out, when the data is
         // discarded anyway; keep the warp converged for the aligned tcgen05 ops.
         if constexpr (!kEarlyDrain) {
-          tmem_ld_wait();
-          // This warp's part of the accumulator is read: hand it back to the UMMA issuer.
-          if (c == kChunksPerWarp - 1) release_accumulator();
+          tmem_ld_wait();  // this chunk is in registers (nothing else is in flight)
+          if (c + 1 < kChunksPerWarp) load_chunk(c + 1, racc[2 * (kPb ^ 1u)], racc[2 * (kPb ^ 1u) + 1]);
+          else release_accumulator();  // this warp's part of the accumulator is read: hand it back
         }
 #pragma unroll
         for (uint32_t h = 0; h < 2; ++h) {
-          const uint32_t(&r)[32] = racc[kEarlyDrain ? 2 * c + h : h];
+          const uint32_t(&r)[32] = racc[kEarlyDrain ? 2 * c + h : 2 * kPb + h];
 #pragma unroll
           for (uint32_t jj = 0; jj < 4; ++jj) {
             const uint32_t j = 4u * h + jj;  // 16-byte chunk of the 128-byte row
             uint8_t* addr = gbuf + lane * 128u + ((j ^ (lane & 7u)) << 4);
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = alpha * __uint_as_float(r[8 * jj + e]);
-            if (load_c) {
-              const uint4 old = *reinterpret_cast<const uint4*>(addr);
-              const __half2* oh = reinterpret_cast<const __half2*>(&old);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = __half22float2(oh[e]);
-                v[2 * e] = fmaf(beta, f.x, v[2 * e]);
-                v[2 * e + 1] = fmaf(beta, f.y, v[2 * e + 1]);
-              }
-            }
+            // alpha * acc (+ beta * old C) on pairs of fp32 values (fma.rn.f32x2: one instruction per
+            // pair, each half rounded as the scalar operation would be), then one conversion per pair
             uint4 out;
-            __half2* ph = reinterpret_cast<__half2*>(&out);
+            uint32_t* po = reinterpret_cast<uint32_t*>(&out);
+            uint4 old = make_uint4(0u, 0u, 0u, 0u);
+            if (load_c) old = *reinterpret_cast<const uint4*>(addr);
+            const uint32_t* oldw = reinterpret_cast<const uint32_t*>(&old);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) ph[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+            for (int e = 0; e < 4; ++e) {
+              uint64_t v = pack_f32x2(r[8 * jj + 2 * e], r[8 * jj + 2 * e + 1]);
+              if (!alpha_one) v = mul_f32x2(alpha2, v);
+              if (load_c) v = fma_f32x2(beta2, half2_to_f32x2(oldw[e]), v);
+              po[e] = f32x2_to_half2(v);
+            }
             *reinterpret_cast<uint4*>(addr) = out;
           }
         }
@@ -493,12 +532,29 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (tracer) trace_stamp(p.trace, local_tile, 5 + (c == 0 ? 0 : 1));
         ok = __all_sync(0xffffffffu, ok);
       };
+      using P0 = std::integral_constant<uint32_t, 0>;
+      using P1 = std::integral_constant<uint32_t, 1>;
       if constexpr (kEarlyDrain) {  // unrolled: the register copy of the accumulator is indexed statically
 #pragma unroll
-        for (uint32_t c = 0; c < kChunksPerWarp; ++c) do_chunk(c);
+        for (uint32_t c = 0; c < kChunksPerWarp; ++c) do_chunk(c, P0{});
       } else {
+        static_assert(kEarlyDrain || kChunksPerWarp % 2 == 0, "chunks are taken in pairs");
 #pragma unroll 1
-        for (uint32_t c = 0; c < kChunksPerWarp; ++c) do_chunk(c);
+        for (uint32_t c = 0; c < kChunksPerWarp; c += 2) {
+          do_chunk(c, P0{});
+          do_chunk(c + 1, P1{});
+        }
+      }
+    }
+    if (!ok) {
+      // After a time-out: leave only when the loads of old C still in flight have landed
+      // (a short bounded wait per buffer).
+      for (uint32_t b = 0; b < (uint32_t)L::kBufsPerWarp; ++b) {
+        if (c_in_flight & (1u << b)) {
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(cload_bar(epi_w, b), (cphase >> b) & 1u) && global_timer_ns() - t0 < MMBO_DRAIN_LIMIT_NS) {
+          }
+        }
       }
     }
     if (lane == 0) tma_store_wait_all<0>();

@@ -46,7 +46,7 @@ static const KernelRow kF16Rows[] = {
     {"hgemm_tcgen05_MT256x128x64_S4_CG1_WG192_WGM08", 256, 128, 192, 64, 4, 1, 8, 1},
     {"hgemm_tcgen05_MT128x128x64_S6_CG1_WG192_WGM08", 128, 128, 192, 64, 6, 1, 8, 1},
     {"hgemm_tcgen05_MT256x256x64_S6_CG2_WG192_WGM08", 256, 256, 192, 64, 6, 2, 8, 1},
-    {"hgemm_tcgen05_MT256x256x64_S5_CG2_WG320_WGM08", 256, 256, 320, 64, 5, 2, 8, 1},
+    {"hgemm_tcgen05_MT256x256x64_S3_CG2_WG320_WGM08", 256, 256, 320, 64, 3, 2, 8, 1},
 };
 // fp64 rows (the reference's own dtype).
 static const KernelRow kF64Rows[] = {
@@ -598,7 +598,7 @@ static int select_f16(const GemmArgs& g) {
   const double s3 = 1.00 * eff(t3, sms / 2) * fill(t3, 256, 256);
   // Short contractions are bound by how fast accumulators are drained: the variant with
   // eight epilogue warps wins there and ties on long ones.
-  if (s3 >= s1 && s3 >= s2) return g.k <= 1536 ? 4 : 3;
+  if (s3 >= s1 && s3 >= s2) return g.k <= 1024 ? 4 : 3;
   return s1 >= s2 ? 1 : 2;
 }
 
@@ -721,7 +721,7 @@ static int run_f16(const GemmArgs& g_in, int id, cudaStream_t st) {
     case 1: return launch_hgemm_tcgen05<256, 4, 1>(g, env_u32("MMBO_WGM", kF16Rows[1].wgm), st);
     case 2: return launch_hgemm_tcgen05<128, 6, 1>(g, env_u32("MMBO_WGM", kF16Rows[2].wgm), st);
     case 3: return launch_hgemm_tcgen05<256, 6, 2>(g, env_u32("MMBO_WGM", kF16Rows[3].wgm), st);
-    case 4: return launch_hgemm_tcgen05<256, 5, 2, 8>(g, env_u32("MMBO_WGM", kF16Rows[4].wgm), st);
+    case 4: return launch_hgemm_tcgen05<256, 3, 2, 8>(g, env_u32("MMBO_WGM", kF16Rows[4].wgm), st);
   }
   return MMBO_ERR_BAD_KERNEL_ID;
 }

@@ -129,6 +129,39 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// ---------------------------------------------------------------- packed fp32 ---------
+// Two fp32 values in one 64-bit register; sm_100 multiplies and fuses them in one instruction
+// (each half is rounded exactly as the scalar instruction would round it).
+__device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+// {lo, hi} fp16 pair (lo in the low 16 bits, as stored in memory) <-> packed fp32 pair
+__device__ __forceinline__ uint64_t half2_to_f32x2(uint32_t h2) {
+  uint32_t lo, hi;
+  asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}"
+      : "=r"(lo), "=r"(hi)
+      : "r"(h2));
+  return pack_f32x2(lo, hi);
+}
+__device__ __forceinline__ uint32_t f32x2_to_half2(uint64_t v) {
+  uint32_t lo, hi, r;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "r"(hi), "r"(lo));  // first source -> upper half
+  return r;
+}
+
 // ---------------------------------------------------------------- fences -------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
