@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ptx.cuh"
 #include "raster.h"
 
 namespace mmbo {
@@ -133,11 +134,13 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
   mmbo_wgm_remap(blockIdx.x, blockIdx.y, gridDim.x, gridDim.y, p.wgm, &tile_m, &tile_n);
   const uint32_t m0 = tile_m * BM, n0 = tile_n * BN;
 
-  float acc[TTN][TTM];
+  // Accumulators as packed pairs along m: one fma.rn.f32x2 updates two of them, so the 64
+  // FMAs of a k step take 32 issue slots and leave room for the loads and the loop.
+  uint64_t acc2[TTN][TTM / 2];
 #pragma unroll
   for (int j = 0; j < TTN; ++j)
 #pragma unroll
-    for (int i = 0; i < TTM; ++i) acc[j][i] = 0.f;
+    for (int i = 0; i < TTM / 2; ++i) acc2[j][i] = 0ull;
 
   float ra[LoadA::kElems], rb[LoadB::kElems];
   const uint32_t num_kb = (p.k + BK - 1) / BK;
@@ -158,11 +161,13 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     const float* __restrict__ b_s = sB[cur];
 #pragma unroll
     for (int l = 0; l < BK; ++l) {
-      float fa[TTM], fb[TTN];
+      uint64_t fa2[TTM / 2];
+      float fb[TTN];
 #pragma unroll
       for (int h = 0; h < HM; ++h) {
-        const float4 x = *reinterpret_cast<const float4*>(a_s + l * PA + h * (BM / HM) + tx * 4);
-        fa[4 * h] = x.x; fa[4 * h + 1] = x.y; fa[4 * h + 2] = x.z; fa[4 * h + 3] = x.w;
+        const uint4 x = *reinterpret_cast<const uint4*>(a_s + l * PA + h * (BM / HM) + tx * 4);
+        fa2[2 * h] = pack_f32x2(x.x, x.y);
+        fa2[2 * h + 1] = pack_f32x2(x.z, x.w);
       }
 #pragma unroll
       for (int h = 0; h < HN; ++h) {
@@ -170,9 +175,11 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
         fb[4 * h] = x.x; fb[4 * h + 1] = x.y; fb[4 * h + 2] = x.z; fb[4 * h + 3] = x.w;
       }
 #pragma unroll
-      for (int j = 0; j < TTN; ++j)
+      for (int j = 0; j < TTN; ++j) {
+        const uint64_t bb = pack_f32x2(__float_as_uint(fb[j]), __float_as_uint(fb[j]));
 #pragma unroll
-        for (int i = 0; i < TTM; ++i) acc[j][i] = fmaf(fa[i], fb[j], acc[j][i]);
+        for (int i = 0; i < TTM / 2; ++i) acc2[j][i] = fma_f32x2(fa2[i], bb, acc2[j][i]);
+      }
     }
     if (kb + 1 < num_kb) {
       LoadA::store(ra, sA[cur ^ 1], tid);
@@ -184,6 +191,14 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
   // Write-back: C = beta != 0 ? alpha*acc + beta*C : alpha*acc.
   const float alpha = p.alpha, beta = p.beta;
   const bool use_c = beta != 0.f;
+  float acc[TTN][TTM];
+#pragma unroll
+  for (int j = 0; j < TTN; ++j)
+#pragma unroll
+    for (int i = 0; i < TTM / 2; ++i) {
+      acc[j][2 * i] = __uint_as_float((uint32_t)(acc2[j][i] & 0xffffffffull));
+      acc[j][2 * i + 1] = __uint_as_float((uint32_t)(acc2[j][i] >> 32));
+    }
 #pragma unroll
   for (int hn = 0; hn < HN; ++hn)
 #pragma unroll
