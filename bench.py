@@ -283,7 +283,7 @@ def main():
     achieved = 2.0 * m * ncols * k / (kern_avg * 1e-3) / 1e12
     # DRAM bytes per launch from the ncu capture of this workload (dram__bytes_read.sum +
     # dram__bytes_write.sum; summary under profiles/): known for the default N=1 case only
-    traffic = 1.571e9 if (P == 1 and (m, n, k) == (8192, 8192, 8192) and args.kernel in (-1, 3)) else None
+    traffic = 1.805e9 if (P == 1 and (m, n, k) == (8192, 8192, 8192) and args.kernel in (-1, 3)) else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": traffic,
                 "algorithmic_bytes": 2.0 * (m * k + k * ncols + m * ncols * (2 if w["beta"] else 1)),
