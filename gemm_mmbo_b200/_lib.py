@@ -24,6 +24,9 @@ SIGNATURES = {
                                      _fp, _vp, _sz, ctypes.c_int, _vp]),
     "mmbo_gemm_f16": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
                                      _fp, _vp, _sz, ctypes.c_int, _vp]),
+    "mmbo_gemm_f16_bcast": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
+                                           _fp, _vp, _sz, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+                                           ctypes.c_int, _vp]),
     "mmbo_gemm_f64": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _dp, _vp, _sz, _vp, _sz,
                                      _dp, _vp, _sz, ctypes.c_int, _vp]),
     "mmbo_fill_f64": (ctypes.c_int, [_vp, _sz, _sz, _sz, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int,

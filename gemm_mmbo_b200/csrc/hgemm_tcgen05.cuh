@@ -93,6 +93,18 @@ struct HgemmParams {
                    // into the padding rows below the matrix)
 };
 
+// Destinations beyond C itself: the same window of C in the memory of other GPUs of the node
+// (peer mappings).  The epilogue stores every finished chunk to each of them with one more TMA
+// store from the same staging buffer, so that a column-sharded GEMM leaves the assembled
+// matrix on every GPU without a separate all-gather (stores only: nothing is ever loaded
+// through these maps).
+constexpr int kMaxPeerCopies = 7;
+struct alignas(64) HgemmPeerMaps {
+  CUtensorMap map[kMaxPeerCopies];
+  uint32_t count;
+  uint32_t pad[15];
+};
+
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -115,7 +127,8 @@ template <int TM, int STAGES, bool A_KMAJOR, bool B_KMAJOR, int CG = 1, int EW =
 __global__ void __launch_bounds__(64 + 32 * EW, 1)
 hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b,
-                     const __grid_constant__ CUtensorMap tmap_c, const HgemmParams p) {
+                     const __grid_constant__ CUtensorMap tmap_c, const HgemmParams p,
+                     const __grid_constant__ HgemmPeerMaps peers) {
   using L = HgemmSmem<TM, STAGES, CG, EW>;
   static_assert(TM == 128 || TM == 256, "TM is the UMMA N extent");
   static_assert(EW == 4 || EW == 8, "one or two epilogue warps per tensor-memory quarter");
@@ -509,9 +522,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           __syncwarp();
           if (tracer && c == 0) trace_stamp(p.trace, local_tile, 12);  // fenced
           if (lane == 0) {
-            if (in_range && ok && (p.diag & 1u) == 0u)
+            if (in_range && ok && (p.diag & 1u) == 0u) {
               tma_store_2d(&tmap_c, sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
-            tma_store_commit();
+              for (uint32_t d = 0; d < peers.count; ++d)  // the same chunk into every peer's copy of C
+                tma_store_2d(&peers.map[d], sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
+            }
+            tma_store_commit();  // one group: the buffer is free again when all of them have read it
           }
         } else {
           __syncwarp();

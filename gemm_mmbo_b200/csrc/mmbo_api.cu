@@ -121,6 +121,9 @@ struct GemmArgs {
   void* C;
   size_t lda, ldb, ldc;
   float alpha, beta;
+  // fp16 tensor-core kernels only: further copies of the C window (peer GPUs) the epilogue stores to
+  void* const* peers = nullptr;
+  int npeers = 0;
 };
 
 static int validate(const GemmArgs& g, const float* alpha, const float* beta) {
@@ -258,7 +261,7 @@ static bool hgemm_tma_ok(const GemmArgs& g) {
 
 template <int TM, int STAGES, int CG, int EW, bool AK, bool BK_>
 static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                             const HgemmParams& p, uint64_t tiles, cudaStream_t st) {
+                             const HgemmParams& p, const HgemmPeerMaps& peers, uint64_t tiles, cudaStream_t st) {
   using L = HgemmSmem<TM, STAGES, CG, EW>;
   auto kern = hgemm_tcgen05_kernel<TM, STAGES, AK, BK_, CG, EW>;
   static bool attr_done[kMaxDevices] = {};
@@ -297,7 +300,7 @@ static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
+  return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p, peers);
 }
 
 template <int TM, int STAGES, int CG, int EW = 4>
@@ -324,6 +327,17 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   } else {
     tc = ta;  // placeholder, never dereferenced by the plain epilogue
   }
+  static HgemmPeerMaps peers;  // (callers hold the library lock)
+  peers.count = 0;
+  if (g.npeers > 0) {
+    if (!c_tma || g.npeers > kMaxPeerCopies) return MMBO_ERR_KERNEL_UNSUITABLE;  // peer copies go through TMA stores only
+    for (int d = 0; d < g.npeers; ++d) {
+      if (!g.peers[d] || !aligned16(g.peers[d])) return MMBO_ERR_KERNEL_UNSUITABLE;
+      rc = make_map_2d(&peers.map[d], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.peers[d], g.m, g.n, g.ldc, 64, 32);
+      if (rc) return rc;
+    }
+    peers.count = (uint32_t)g.npeers;
+  }
 
   HgemmParams p;
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
@@ -336,10 +350,10 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   p.diag = env_u32("MMBO_DIAG", 0);  // diagnostic builds (no C store / no drain): never set in production
   const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
   if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-  if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, true>(ta, tb, tc, p, tiles, st);
-  if (g.transA && g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, false>(ta, tb, tc, p, tiles, st);
-  if (!g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, false, true>(ta, tb, tc, p, tiles, st);
-  return launch_hgemm_inst<TM, STAGES, CG, EW, false, false>(ta, tb, tc, p, tiles, st);
+  if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, true>(ta, tb, tc, p, peers, tiles, st);
+  if (g.transA && g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, false>(ta, tb, tc, p, peers, tiles, st);
+  if (!g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, false, true>(ta, tb, tc, p, peers, tiles, st);
+  return launch_hgemm_inst<TM, STAGES, CG, EW, false, false>(ta, tb, tc, p, peers, tiles, st);
 }
 
 // ------------------------------------------------------------------ scratch memory --
@@ -880,6 +894,28 @@ int mmbo_gemm_f16(int transA, int transB, size_t m, size_t n, size_t k, const fl
   g.beta = *beta;
   if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF16)) return MMBO_ERR_BAD_KERNEL_ID;
   const int id = kernelId == MMBO_KERNEL_AUTO ? select_f16(g) : kernelId;
+  return run_f16(g, id, static_cast<cudaStream_t>(stream));
+}
+
+int mmbo_gemm_f16_bcast(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha, const void* A,
+                        size_t lda, const void* B, size_t ldb, const float* beta, void* C, size_t ldc,
+                        void* const* C_peers, int npeers, int kernelId, void* stream) {
+  MMBO_API_LOCK();
+  GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
+  int rc = validate(g, alpha, beta);
+  if (rc) return rc;
+  g.alpha = *alpha;
+  g.beta = *beta;
+  if (npeers < 0 || npeers > kMaxPeerCopies) return MMBO_ERR_BAD_DIM;
+  if (npeers > 0 && !C_peers) return MMBO_ERR_NULL_POINTER;
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 1 || kernelId >= kNumF16)) return MMBO_ERR_BAD_KERNEL_ID;
+  if (g.m == 0 || g.n == 0) return MMBO_OK;
+  // only the tensor-core kernels with the TMA epilogue can store to further destinations
+  if (g.k == 0 || !hgemm_tma_ok(g) || !aligned16(g.C) || g.ldc % 8 != 0 || g.m % 8 != 0) return MMBO_ERR_KERNEL_UNSUITABLE;
+  int id = kernelId == MMBO_KERNEL_AUTO ? select_f16(g) : kernelId;
+  if (id == 0) id = 2;  // the smallest tensor-core tile instead of the one-thread-per-element kernel
+  g.peers = C_peers;
+  g.npeers = npeers;
   return run_f16(g, id, static_cast<cudaStream_t>(stream));
 }
 

@@ -69,6 +69,19 @@ def gemm(dtype, transA: bool, transB: bool, m: int, n: int, k: int, alpha: float
         raise MmboError(rc, name)
 
 
+def gemm_bcast(transA: bool, transB: bool, m: int, n: int, k: int, alpha: float, A, lda: int, B, ldb: int,
+               beta: float, C, ldc: int, peers, kernelId: int = KERNEL_AUTO, stream=None) -> None:
+    """fp16 GEMM whose epilogue also stores the result to further copies of the C window
+    (`peers`: addresses or tensors, e.g. the same window in other GPUs' memory)."""
+    a, b = ctypes.c_float(alpha), ctypes.c_float(beta)
+    arr = (ctypes.c_void_p * max(1, len(peers)))(*[_addr(p) for p in peers])
+    rc = LIB.mmbo_gemm_f16_bcast(int(bool(transA)), int(bool(transB)), m, n, k, ctypes.byref(a), _addr(A), lda,
+                                 _addr(B), ldb, ctypes.byref(b), _addr(C), ldc, arr, len(peers), kernelId,
+                                 _stream(stream))
+    if rc != 0:
+        raise MmboError(rc, "mmbo_gemm_f16_bcast")
+
+
 def gemm_host(dtype, transA: bool, transB: bool, m: int, n: int, k: int, alpha: float, A, lda: int, B,
               ldb: int, beta: float, C, ldc: int, kernelId: int = KERNEL_AUTO) -> None:
     """Same GEMM with A, B, C in host memory (pinned torch tensors, numpy arrays or raw

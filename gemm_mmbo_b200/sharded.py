@@ -3,8 +3,11 @@
 The contraction needs no communication: rank r owns columns [col0, col0 + ncols) of
 op(B) and of C, every rank holds all of A, and each rank runs an independent
 m x ncols x k GEMM through the library's C ABI.  The only exchange step is optional:
-reassembling the full C on every rank with an all-gather of the column blocks (NCCL
-over NVLink when the tensors are on GPUs).  The reference has no multi-device path
+reassembling the full C on every rank.  On GPUs that is fused into the GEMM: the full C
+lives in symmetric memory (every rank maps every other rank's copy) and the epilogue of
+the tensor-core kernel stores each finished chunk into all copies over NVLink
+(`gemm_and_broadcast`, fp16); an all-gather of the column blocks (NCCL, or gloo for CPU
+tensors) remains as the plain alternative.  The reference has no multi-device path
 (device index hard-coded: src/gemm/benchmark.cc:54); this is new capability behind
 the same GEMM call.
 
@@ -102,6 +105,42 @@ class ColumnShard:
                 self.gather(C_block, C_full, m, group, begin, cnt)
             begin += cnt
         compute.wait_stream(comm)
+
+
+    # ---- exchange fused into the GEMM -------------------------------------------------------
+    def gemm_and_broadcast(self, transA, transB, m, k, alpha, A, lda, B_block, ldb, beta, C_sym: "SymmetricC",
+                           kernelId=_g.KERNEL_AUTO, stream=None, barrier: bool = True):
+        """fp16 GEMM on this rank's column block whose epilogue writes the block into the full
+        C of every rank (C_sym).  With beta != 0 the old values are taken from this rank's
+        copy.  `barrier`: wait (on the stream) until every rank's GEMM has finished, after
+        which the whole of C is valid on this rank."""
+        off = self.col0 * m * 2  # bytes to column col0 of the (n, m) fp16 array, leading dimension m
+        mine = C_sym.ptrs[self.rank] + off
+        peers = [p + off for r, p in enumerate(C_sym.ptrs) if r != self.rank]
+        _g.gemm_bcast(transA, transB, m, self.ncols, k, alpha, A, lda, B_block, ldb, beta, mine, m, peers, kernelId,
+                      stream)
+        if barrier:
+            C_sym.barrier()
+
+
+class SymmetricC:
+    """The full column-major C (n columns of m fp16 elements) allocated in symmetric memory:
+    `tensor` is this rank's copy, `ptrs[r]` the address at which rank r's copy is mapped into
+    this process.  Collective: every rank of `group` constructs it at the same time."""
+
+    def __init__(self, n: int, m: int, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        group = dist.group.WORLD if group is None else group
+        self.tensor = symm_mem.empty((n, m), dtype=torch.float16, device=torch.device("cuda", torch.cuda.current_device()))
+        self._hdl = symm_mem.rendezvous(self.tensor, group)
+        self.ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+        self.rank, self.world = self._hdl.rank, self._hdl.world_size
+
+    def barrier(self):
+        """All ranks' work queued so far on their current streams has finished (stream-ordered)."""
+        self._hdl.barrier()
 
 
 _SIDE = {}

@@ -71,6 +71,21 @@ int mmbo_gemm_f16(int transA, int transB, size_t m, size_t n, size_t k, const fl
                   const void* A, size_t lda, const void* B, size_t ldb, const float* beta,
                   void* C, size_t ldc, int kernelId, void* stream);
 
+/* HGEMM whose result is written to C and, chunk by chunk from the same epilogue, to `npeers`
+ * (0..7) further copies of the same window of C: C_peers[i] is the address of C(0,0) in copy i,
+ * same ldc.  Meant for copies that live on other GPUs of the node (peer mappings): a GEMM
+ * sharded by column blocks then leaves the assembled C on every GPU without a separate
+ * all-gather.  With beta != 0 the old values are read from C only.  Needs the tensor-core
+ * kernels with the TMA epilogue: 16-byte aligned A, B, C and copies, lda, ldb, ldc multiples
+ * of 8, m a multiple of 8, k > 0; otherwise MMBO_ERR_KERNEL_UNSUITABLE.  The copies are complete when
+ * the stream reaches the end of the call; telling the other GPUs so is the caller's
+ * business (a barrier across ranks).  No counterpart in the reference, which drives one GPU
+ * (device index fixed: src/gemm/benchmark.cc:54). */
+int mmbo_gemm_f16_bcast(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
+                        const void* A, size_t lda, const void* B, size_t ldb, const float* beta,
+                        void* C, size_t ldc, void* const* C_peers, int npeers, int kernelId,
+                        void* stream);
+
 /* The same GEMMs on operands in HOST memory: A, B, C are host pointers (pinned memory
  * gives full copy bandwidth), everything else as above.  This is the whole round trip
  * the reference's harness performs around its kernel (device allocation, hipMemcpy in,

@@ -136,3 +136,40 @@ def test_hgemm_c_with_odd_leading_dim(cuda, mm, oracle):
     assert mm.select_kernel("f16", False, True, m, n, k, dA, case.lda, dB, case.ldb, dC, case.ldc) != 0
     for kid in (1, 2, 3, 4, -1):
         run_and_check(cuda, mm, case, kid)
+
+
+@pytest.mark.parametrize("kernel_id", [-1, 1, 2, 3, 4])
+def test_hgemm_result_stored_to_further_copies(cuda, mm, oracle, kernel_id):
+    """mmbo_gemm_f16_bcast with the further copies on the same GPU: every copy must hold the same
+    bits as C, rows below the matrix untouched; beta != 0 reads the old values from C only."""
+    import numpy as np
+    torch = cuda
+    m, n, k = 520, 392, 328
+    case = Case(oracle, "f16", False, True, m, n, k, 1.0, 0.5, pad=(0, 0, 8), dist=oracle.DIST_NORMAL, scale=0.5)
+    dA = torch.from_numpy(case.A.reshape(-1)).cuda()
+    dB = torch.from_numpy(case.B.reshape(-1)).cuda()
+    dC = torch.from_numpy(case.C.reshape(-1)).cuda()
+    copies = [torch.full((case.C.size,), 7.0, dtype=torch.float16, device="cuda") for _ in range(3)]
+    mm.gemm_bcast(False, True, m, n, k, 1.0, dA, case.lda, dB, case.ldb, 0.5, dC, case.ldc, copies, kernel_id)
+    torch.cuda.synchronize()
+    assert mm.device_status() == 0
+    got = dC.cpu().numpy().reshape(case.C.shape)
+    err = oracle.rel_frobenius("f16", m, n, np.ascontiguousarray(got), case.ldc, case.reference())
+    assert err <= 2e-3, err
+    for c in copies:
+        h = c.cpu().numpy().reshape(case.C.shape)
+        assert np.array_equal(h[:, :m].view(np.uint16), got[:, :m].view(np.uint16))
+        assert (h[:, m:] == 7.0).all(), "padding rows of a copy written"
+
+
+def test_hgemm_bcast_refuses_what_tma_cannot_store(cuda, mm, oracle):
+    torch = cuda
+    m, n, k = 260, 128, 64  # m not a multiple of 8: the TMA epilogue would spill into padding rows
+    A = torch.zeros(264 * k, dtype=torch.float16, device="cuda")
+    B = torch.zeros(n * k, dtype=torch.float16, device="cuda")
+    C = torch.zeros(n * 264, dtype=torch.float16, device="cuda")
+    with pytest.raises(mm.MmboError) as e:
+        mm.gemm_bcast(False, True, m, n, k, 1.0, A, 264, B, n, 0.0, C, 264, [C])
+    assert e.value.status == -8  # MMBO_ERR_KERNEL_UNSUITABLE
+    with pytest.raises(mm.MmboError):
+        mm.gemm_bcast(False, True, 256, n, k, 1.0, A, 256, B, n, 0.0, C, 256, [C] * 8)  # more than 7 copies

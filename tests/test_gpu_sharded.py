@@ -1,6 +1,7 @@
 """Multi-GPU path on real devices (needs >= 2 GPUs, skipped otherwise): two ranks, one
 per GPU, each computes its column block of C through the C ABI; the blocks are
-all-gathered over NCCL (whole and panel-overlapped) and compared with the oracle."""
+all-gathered over NCCL (whole and panel-overlapped), or stored into every rank's copy of C
+by the GEMM's own epilogue (symmetric memory), and compared with the oracle."""
 import os
 import pathlib
 import socket
@@ -55,6 +56,32 @@ def _worker(rank, world, port, q):
                 assert mm.device_status() == 0
                 err = O.rel_frobenius("f16", m, n, full.cpu().numpy(), m, ref)
                 assert err <= 2e-3, (ta, tb, panels, err)
+        # the exchange fused into the GEMM: the epilogue stores this rank's block into every
+        # rank's copy of C (symmetric memory), then a barrier; beta = 0 and beta != 0
+        from gemm_mmbo_b200.sharded import SymmetricC
+        ta, tb = False, True
+        sh = ColumnShard(n, world, rank)
+        A = torch.empty((k, m), dtype=torch.float16, device="cuda")
+        mm.fill("f16", A, m, k, m, mat=0)
+        w = sh.b_window(tb, k)
+        B = torch.empty((w["cols"], w["rows"]), dtype=torch.float16, device="cuda")
+        mm.fill("f16", B, w["rows"], w["cols"], w["rows"], mat=1, row0=w["row0"], col0=w["col0"],
+                total_rows=w["total_rows"])
+        hA, hB, hC = O.fill("f16", m, k, mat=0), O.fill("f16", n, k, mat=1), O.fill("f16", m, n, mat=2)
+        sym = SymmetricC(n, m)
+        for beta in (0.0, 0.5):
+            if beta == 0.0:
+                sym.tensor.fill_(float("nan"))
+            else:
+                mm.fill("f16", sym.tensor, m, n, m, mat=2)
+            sym.barrier()
+            sh.gemm_and_broadcast(ta, tb, m, k, 1.0, A, m, B, w["rows"], beta, sym)
+            torch.cuda.synchronize()
+            assert mm.device_status() == 0
+            ref = O.gemm("f16", ta, tb, m, n, k, 1.0, hA, m, hB, n, beta, hC if beta else None, m)
+            err = O.rel_frobenius("f16", m, n, sym.tensor.cpu().numpy(), m, ref)
+            assert err <= 2e-3, ("fused", beta, err)
+            sym.barrier()
         q.put((rank, "ok"))
     except Exception as e:
         q.put((rank, f"{type(e).__name__}: {e}"))
