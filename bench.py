@@ -9,7 +9,9 @@ A step is one GEMM call through the library's C ABI on synthetic seeded operands
          (the configuration the headline metric is quoted on);
   N > 1  HGEMM NN, M=N=K=32768, alpha=1, beta=0, U[-1,1): B and C split into N column
          blocks, A replicated, one rank per GPU, no communication in the contraction
-         (--gather adds an all-gather of the C blocks after each GEMM).
+         (--gather: the GEMM's epilogue also stores each rank's block into every rank's copy of
+         C over NVLink, so that each step ends with the whole C on every GPU; --gather-nccl: the
+         same through an overlapped NCCL all-gather).
 
 `value` is whole-job TFLOP/s (2*M*N*K per step over the slowest rank's device time) with
 operands resident in HBM; `e2e` is the same metric with pinned host operands copied to
@@ -40,7 +42,11 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--gather", action="store_true", help="N>1: all-gather C after every GEMM")
+    ap.add_argument("--gather", action="store_true",
+                    help="N>1: every rank ends each step with the whole C (the GEMM's epilogue stores its block "
+                         "into all ranks' copies over NVLink)")
+    ap.add_argument("--gather-nccl", action="store_true",
+                    help="N>1: the same result through an NCCL all-gather overlapped with the GEMM in 4 panels")
     ap.add_argument("--kernel", type=int, default=-1, help="force a kernel id of the fp16 table")
     ap.add_argument("--size", type=int, default=0, help="override M=N=K (debugging / profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -221,15 +227,19 @@ def main():
     else:    # B stored k x n: the block is a column window
         mm.fill("f16", B, rb, cb, rb, mat=1, dist=w["dist"], scale=w["scale"], col0=col0, total_rows=k)
     mm.fill("f16", C, m, ncols, m, mat=2, dist=w["dist"], scale=w["scale"], col0=col0, total_rows=m)
-    Cfull = torch.empty((n, m), dtype=torch.float16, device="cuda") if (args.gather and P > 1) else None
-
+    Cfull = torch.empty((n, m), dtype=torch.float16, device="cuda") if (args.gather_nccl and P > 1) else None
+    Csym = None
     shard = None
-    if Cfull is not None:
-        from gemm_mmbo_b200.sharded import ColumnShard
+    if P > 1 and (args.gather or args.gather_nccl):
+        from gemm_mmbo_b200.sharded import ColumnShard, SymmetricC
         shard = ColumnShard(n, P, rank)
+        if Cfull is None:
+            Csym = SymmetricC(n, m)  # every rank's copy of the whole C, mapped into every rank
 
     def step():
-        if shard is not None:  # GEMM in column panels, each panel's all-gather overlapped
+        if Csym is not None:  # the epilogue stores this rank's block into every rank's C, then a barrier
+            shard.gemm_and_broadcast(ta, tb, m, k, w["alpha"], A, ra, B, rb, w["beta"], Csym, kernelId=args.kernel)
+        elif shard is not None:  # GEMM in column panels, each panel's all-gather overlapped
             shard.gemm_and_gather("f16", ta, tb, m, k, w["alpha"], A, ra, B, rb, w["beta"], C, Cfull,
                                   panels=4, kernelId=args.kernel)
         else:
@@ -275,7 +285,7 @@ def main():
         kern_ms.append(a.elapsed_time(b))
     isolated_ms = sum(kern_ms) / len(kern_ms)
     # average launch duration over the timed region (back-to-back launches of this rank)
-    kern_avg = ev0.elapsed_time(ev1) / args.steps if not args.gather else isolated_ms
+    kern_avg = ev0.elapsed_time(ev1) / args.steps if shard is None else isolated_ms
     peaks = measured_peaks()
     # the timed region is a loop of back-to-back launches: sustained when it lasts
     # seconds, burst otherwise
@@ -341,7 +351,9 @@ def main():
             "scaling": "strong" if P > 1 else "weak", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic",
             "config": {"workload": w["name"], "m": m, "n": n, "k": k, "columns_per_gpu": ncols,
-                       "gather_c": bool(Cfull is not None), "l2": "inputs larger than L2 (126 MB)",
+                       "gather_c": ("fused: epilogue stores to every GPU's C" if Csym is not None else
+                                    "NCCL all-gather, 4 panels" if Cfull is not None else False),
+                       "l2": "inputs larger than L2 (126 MB)",
                        "accumulate": "fp32"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps, "roofline": roofline,
             "cpu_baseline": cpu, "impl": "ours",
