@@ -126,3 +126,31 @@ def test_gather_reports_an_absent_rank_instead_of_hanging():
             p.kill()
     assert results[1] == "absent"
     assert results[0].startswith("error after"), results
+
+
+def test_broadcast_addresses_cover_every_copy(monkeypatch):
+    """gemm_and_broadcast hands the GEMM this rank's window in its own copy of C and the same
+    window in every other rank's copy (no GPU: the C ABI call is intercepted)."""
+    sys.path.insert(0, str(ROOT))
+    import importlib
+    sharded = importlib.import_module("gemm_mmbo_b200.sharded")
+    calls = []
+    monkeypatch.setattr(sharded._g, "gemm_bcast", lambda *a: calls.append(a))
+
+    class FakeC:
+        ptrs = [0x10000000, 0x20000000, 0x30000000, 0x40000000]
+        barriers = 0
+
+        def barrier(self):
+            FakeC.barriers += 1
+
+    n, m, k, world = 4096, 512, 64, 4
+    for rank in range(world):
+        sh = sharded.ColumnShard(n, world, rank)
+        sh.gemm_and_broadcast(False, True, m, k, 1.0, 111, m, 222, sh.ncols, 0.0, FakeC())
+        (ta, tb, mm_, nn, kk, alpha, A, lda, B, ldb, beta, C, ldc, peers, kid, stream) = calls[-1]
+        off = sh.col0 * m * 2
+        assert (mm_, nn, kk, ldc) == (m, sh.ncols, k, m)
+        assert C == FakeC.ptrs[rank] + off
+        assert peers == [p + off for r, p in enumerate(FakeC.ptrs) if r != rank]
+    assert FakeC.barriers == world
