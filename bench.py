@@ -234,7 +234,18 @@ def main():
         from gemm_mmbo_b200.sharded import ColumnShard, SymmetricC
         shard = ColumnShard(n, P, rank)
         if Cfull is None:
-            Csym = SymmetricC(n, m)  # every rank's copy of the whole C, mapped into every rank
+            try:
+                Csym = SymmetricC(n, m)  # every rank's copy of the whole C, mapped into every rank
+                ok = torch.ones(1, device="cuda")
+            except Exception as e:  # no symmetric memory on this system: all ranks fall back together
+                if rank == 0:
+                    print(f"bench.py: symmetric memory unavailable ({type(e).__name__}: {e}); using the NCCL all-gather",
+                          file=sys.stderr)
+                ok = torch.zeros(1, device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if float(ok.item()) == 0.0:
+                Csym = None
+                Cfull = torch.empty((n, m), dtype=torch.float16, device="cuda")
 
     def step():
         if Csym is not None:  # the epilogue stores this rank's block into every rank's C, then a barrier
