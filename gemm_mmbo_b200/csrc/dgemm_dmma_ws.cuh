@@ -3,7 +3,7 @@
 // The fp64 tensor pipe (mma.sync.m8n8k4.f64, 256 FMAs per warp instruction) is shared with
 // nothing else a GEMM needs, so the kernel is arranged so that the four warps that issue it
 // do nothing but load fragments from shared memory and multiply:
-//   * a producer warpgroup (four warps, 40 registers each after setmaxnreg) fills a ring of
+//   * a producer warpgroup (four warps, 48 registers each after setmaxnreg) fills a ring of
 //     kWsStages operand slabs (depth 16) and never computes.  Where an operand's tile rows are
 //     contiguous in memory and 16-byte aligned (op(A) of the N modes, op(B) of the T modes:
 //     both operands of the reference's dgemm_NT) each k-row of the slab is one bulk
@@ -13,9 +13,10 @@
 //     on the way in and zero-fill outside the matrix.  Either way completion is counted on the
 //     slab's "full" mbarrier; consumers hand slabs back through "empty" mbarriers.  There is
 //     no block-wide barrier in the main loop;
-//   * a consumer warpgroup (four warps, 216 registers each), every warp owning a 64 x 32
+//   * a consumer warpgroup (four warps, 208 registers each), every warp owning a 64 x 32
 //     piece of the 128 x 64 tile (64 accumulator doubles per thread, 12 fragment loads per
-//     32 tensor instructions).  The registers taken from the producers let the epilogue keep
+//     32 tensor instructions); a second instantiation with 64 x 64 tiles (32 x 32 per warp)
+//     serves problems that have too few 128-row tiles to fill the machine.  The registers taken from the producers let the epilogue keep
 //     32 values of C in flight per thread, so that reading C costs two memory round trips per
 //     tile instead of one per value;
 //   * two CTAs per SM, each walking tiles of the remapped order (raster.h) with a stride of
@@ -37,11 +38,19 @@
 
 namespace mmbo {
 
-constexpr int kWsBM = 128, kWsBN = 64, kWsBK = 16, kWsStages = 4;
+// Tile rows BM = 128 (warp tile 64 x 32) or 64 (warp tile 32 x 32, for problems with too few 128-row tiles
+// to fill the machine twice).
+constexpr int kWsBN = 64, kWsBK = 16, kWsStages = 4;
 constexpr int kWsConsumers = 4, kWsProducers = 4, kWsThreads = (kWsConsumers + kWsProducers) * 32;
-constexpr int kWsPitchA = kWsBM + 4, kWsPitchB = kWsBN + 4;  // doubles; +4 keeps fragment loads conflict-free
-constexpr int kWsSlabA = kWsBK * kWsPitchA, kWsSlabB = kWsBK * kWsPitchB;
-constexpr size_t kWsSmemBytes = (size_t)kWsStages * (kWsSlabA + kWsSlabB) * sizeof(double);
+constexpr int kWsPitchB = kWsBN + 4;  // doubles; +4 keeps fragment loads conflict-free
+constexpr int kWsSlabB = kWsBK * kWsPitchB;
+template <int BM>
+struct WsTile {
+  static constexpr int kPitchA = BM + 4;
+  static constexpr int kSlabA = kWsBK * kPitchA;
+  static constexpr size_t kSmemBytes = (size_t)kWsStages * (kSlabA + kWsSlabB) * sizeof(double);
+  static constexpr int kFragM = BM / 16;  // m8 fragments per consumer warp (two warps along m)
+};
 // arrivals that complete a slab: one cp.async arrival per producer lane + the expect_tx arrival
 constexpr uint32_t kWsFullCount = kWsProducers * 32 + 1;
 
@@ -98,10 +107,13 @@ __device__ __forceinline__ void ws_fill_elements(uint32_t slab, const double* __
   }
 }
 
-template <bool TRANS_A, bool TRANS_B>
+template <bool TRANS_A, bool TRANS_B, int BM>
 __global__ void __launch_bounds__(kWsThreads, 2)
 dgemm_dmma_ws_kernel(const double* __restrict__ A, const double* __restrict__ B, double* __restrict__ C,
                      const DgemmParams p) {
+  using T = WsTile<BM>;
+  constexpr int kWsBM = BM, kWsPitchA = T::kPitchA, kWsSlabA = T::kSlabA, kFragM = T::kFragM;
+  static_assert(BM == 128 || BM == 64, "two consumer warps along m, 64 or 32 rows each");
   extern __shared__ __align__(128) double ws_smem[];
   __shared__ __align__(8) uint64_t full_bar[kWsStages], empty_bar[kWsStages];
   __shared__ uint32_t abort_flag;
@@ -214,15 +226,15 @@ dgemm_dmma_ws_kernel(const double* __restrict__ A, const double* __restrict__ B,
   // -------------------------------------------------------------------- consumers ----
   asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
   const int gid = lane >> 2, tig = lane & 3;                // fragment coordinates of m8n8k4
-  const int wm = (warp & 1) * 64, wn = (warp >> 1) * 32;    // this warp's 64 x 32 piece of the tile
+  const int wm = (warp & 1) * (BM / 2), wn = (warp >> 1) * 32;  // this warp's (BM / 2) x 32 piece of the tile
   const double alpha = p.alpha, beta = p.beta;
   for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
     uint32_t tile_m, tile_n;
     mmbo_tile_from_serial(tile, tiles_m, tiles_n, p.wgm, &tile_m, &tile_n);
     const uint32_t m0 = tile_m * kWsBM, n0 = tile_n * kWsBN;
-    double acc[8][4][2];
+    double acc[kFragM][4][2];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < kFragM; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
 
@@ -232,13 +244,13 @@ dgemm_dmma_ws_kernel(const double* __restrict__ A, const double* __restrict__ B,
       const double* __restrict__ b_s = ws_smem + kWsStages * kWsSlabA + stage * kWsSlabB + wn + gid;
 #pragma unroll
       for (int k4 = 0; k4 < kWsBK; k4 += 4) {
-        double fa[8], fb[4];
+        double fa[kFragM], fb[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) fa[i] = a_s[(k4 + tig) * kWsPitchA + 8 * i];  // A[m = gid][k = tig]
+        for (int i = 0; i < kFragM; ++i) fa[i] = a_s[(k4 + tig) * kWsPitchA + 8 * i];  // A[m = gid][k = tig]
 #pragma unroll
         for (int j = 0; j < 4; ++j) fb[j] = b_s[(k4 + tig) * kWsPitchB + 8 * j];  // B[k = tig][n = gid]
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < kFragM; ++i)
 #pragma unroll
           for (int j = 0; j < 4; ++j) dmma_m8n8k4(acc[i][j], fa[i], fb[j]);
       }
@@ -255,7 +267,7 @@ dgemm_dmma_ws_kernel(const double* __restrict__ A, const double* __restrict__ B,
       const uint32_t rows_left = p.m > row ? p.m - row : 0u;  // row block i is inside the matrix iff 8i < rows_left
 #pragma unroll
       for (int jh = 0; jh < 2; ++jh) {
-        double old[4][8];
+        double old[4][kFragM];
         double* c_col[4];
         bool col_ok[4];
 #pragma unroll
@@ -268,12 +280,12 @@ dgemm_dmma_ws_kernel(const double* __restrict__ A, const double* __restrict__ B,
 #pragma unroll
           for (int q = 0; q < 4; ++q)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) old[q][i] = (col_ok[q] && 8u * i < rows_left) ? __ldcg(c_col[q] + 8 * i) : 0.0;
+            for (int i = 0; i < kFragM; ++i) old[q][i] = (col_ok[q] && 8u * i < rows_left) ? __ldcg(c_col[q] + 8 * i) : 0.0;
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q)
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < kFragM; ++i) {
             if (!col_ok[q] || 8u * i >= rows_left) continue;
             double r = alpha * acc[i][2 * jh + (q >> 1)][q & 1];
             if (beta != 0.0) r = fma(beta, old[q][i], r);

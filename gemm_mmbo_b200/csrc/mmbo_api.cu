@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <type_traits>
 #include <stdint.h>
 #include <stdio.h>
 
@@ -53,7 +54,8 @@ static const KernelRow kF64Rows[] = {
     {"dgemm_simple_MT032x008x01_TT01_01_WG256", 32, 8, 256, 1, 1, 1, 1, 0},
     {"dgemm_fma_MT064x064x16_TT04_04_WG256_WGM08", 64, 64, 256, 16, 2, 1, 8, 0},
     {"dgemm_dmma_MT128x064x08_WT32_32_WG256_WGM08", 128, 64, 256, 8, 2, 1, 8, 1},
-    {"dgemm_dmma_ws_MT128x064x16_S4_WT64_32_WG160_WGM08", 128, 64, 160, 16, 4, 1, 8, 1},
+    {"dgemm_dmma_ws_MT128x064x16_S4_WT64_32_WG256_WGM08", 128, 64, 256, 16, 4, 1, 8, 1},
+    {"dgemm_dmma_ws_MT064x064x16_S4_WT32_32_WG256_WGM08", 64, 64, 256, 16, 4, 1, 8, 1},
 };
 constexpr int kNumF64 = sizeof(kF64Rows) / sizeof(KernelRow);
 constexpr int kNumF32 = sizeof(kF32Rows) / sizeof(KernelRow);
@@ -637,6 +639,13 @@ static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
   return MMBO_ERR_BAD_KERNEL_ID;
 }
 
+// Default fp64 kernel: the warp-specialised tensor kernel; 64-row tiles while 128-row tiles
+// would not fill the machine's two CTAs per SM twice over.
+static int select_f64(const GemmArgs& g) {
+  const size_t tiles128 = ((g.m + 127) / 128) * ((g.n + kWsBN - 1) / kWsBN);
+  return tiles128 < 4 * (size_t)sm_count() ? 4 : 3;
+}
+
 static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStream_t st) {
   if (g.m == 0 || g.n == 0) return MMBO_OK;
   const double* A = static_cast<const double*>(g.A);
@@ -650,7 +659,7 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
     else gemm_simple_f64_kernel<<<grid, block, 0, st>>>(g.transA, g.transB, g.m, g.n, g.k, alpha, A, g.lda, B, g.ldb, beta, C, g.ldc);
     return (int)cudaGetLastError();
   }
-  if (id < 1 || id > 3) return MMBO_ERR_BAD_KERNEL_ID;
+  if (id < 1 || id > 4) return MMBO_ERR_BAD_KERNEL_ID;
   DgemmParams p;
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
   p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
@@ -666,20 +675,28 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
     else dgemm_dmma_kernel<true, true><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
     return (int)cudaGetLastError();
   }
-  if (id == 3) {  // fp64 tensor path, producer warp + consumer warps, persistent
-    const size_t tiles = ((g.m + kWsBM - 1) / kWsBM) * ((g.n + kWsBN - 1) / kWsBN);
+  if (id == 3 || id == 4) {  // fp64 tensor path, producer and consumer warpgroups, persistent; 128- or 64-row tiles
+    const size_t bm = id == 3 ? 128 : 64;
+    const size_t tiles = ((g.m + bm - 1) / bm) * ((g.n + kWsBN - 1) / kWsBN);
     if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
     const unsigned grid3 = (unsigned)std::min(tiles, (size_t)2 * (size_t)sm_count());  // two CTAs per SM
-    auto launch = [&](auto kernel) -> int {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWsSmemBytes);
+    auto launch = [&](auto kernel, size_t smem) -> int {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
-      kernel<<<grid3, kWsThreads, kWsSmemBytes, st>>>(A, B, C, p);
+      kernel<<<grid3, kWsThreads, smem, st>>>(A, B, C, p);
       return (int)cudaGetLastError();
     };
-    if (!g.transA && !g.transB) return launch(dgemm_dmma_ws_kernel<false, false>);
-    if (!g.transA && g.transB) return launch(dgemm_dmma_ws_kernel<false, true>);
-    if (g.transA && !g.transB) return launch(dgemm_dmma_ws_kernel<true, false>);
-    return launch(dgemm_dmma_ws_kernel<true, true>);
+    auto by_tile = [&](auto ta, auto tb) -> int {
+      constexpr bool TA = decltype(ta)::value, TB = decltype(tb)::value;
+      if (id == 3) return launch(dgemm_dmma_ws_kernel<TA, TB, 128>, WsTile<128>::kSmemBytes);
+      return launch(dgemm_dmma_ws_kernel<TA, TB, 64>, WsTile<64>::kSmemBytes);
+    };
+    using Yes = std::true_type;
+    using No = std::false_type;
+    if (!g.transA && !g.transB) return by_tile(No{}, No{});
+    if (!g.transA && g.transB) return by_tile(No{}, Yes{});
+    if (g.transA && !g.transB) return by_tile(Yes{}, No{});
+    return by_tile(Yes{}, Yes{});
   }
   const size_t gx = (g.m + kDgBM - 1) / kDgBM, gy = (g.n + kDgBN - 1) / kDgBN;
   if (gy > 65535) return MMBO_ERR_TOO_LARGE;
@@ -839,7 +856,7 @@ static int gemm_host(int dtype, const GemmArgs& h, int kernelId, double alpha64 
     if (dtype == MMBO_DTYPE_F64) {
       if (id == MMBO_KERNEL_AUTO) {
         id = tune_lookup(MMBO_DTYPE_F64, g);
-        if (id < 0) id = 3;
+        if (id < 0) id = select_f64(g);
       }
       rc = run_f64(g, alpha64, beta64, id, hp.s_mm);
     } else if (dtype == MMBO_DTYPE_F32) {
@@ -956,7 +973,7 @@ int mmbo_gemm_f64(int transA, int transB, size_t m, size_t n, size_t k, const do
   int id = kernelId;
   if (id == MMBO_KERNEL_AUTO) {
     id = tune_lookup(MMBO_DTYPE_F64, g);
-    if (id < 0) id = 3;  // the fp64 tensor path, warp-specialised
+    if (id < 0) id = select_f64(g);
   }
   return run_f64(g, *alpha, *beta, id, static_cast<cudaStream_t>(stream));
 }
@@ -1036,7 +1053,7 @@ int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, si
   if (dtype == MMBO_DTYPE_F64) {
     if (g.k == 0) return 0;
     const int tuned = tune_lookup(MMBO_DTYPE_F64, g);
-    return tuned >= 0 ? tuned : 3;
+    return tuned >= 0 ? tuned : select_f64(g);
   }
   return MMBO_ERR_BAD_DTYPE;
 }

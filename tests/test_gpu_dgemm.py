@@ -11,7 +11,7 @@ MODES = [(False, False), (False, True), (True, False), (True, True)]
 SHAPES = [(1, 1, 1), (5, 3, 2), (64, 64, 16), (65, 63, 17), (129, 127, 33), (200, 300, 100), (257, 130, 129)]
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, -1])
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_dgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
     for (m, n, k) in SHAPES:
@@ -20,7 +20,7 @@ def test_dgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
             run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4])
 def test_dgemm_beta_zero_and_k_zero(cuda, mm, oracle, kernel_id):
     run_and_check(cuda, mm, Case(oracle, "f64", False, True, 150, 70, 40, 2.0, 0.0, pad=(1, 2, 3), c_poison=True),
                   kernel_id)
@@ -65,7 +65,9 @@ def test_dgemm_persistent_kernel_many_tiles(cuda, mm, oracle, ta, tb):
     m, n, k = 128 * 22 + 10, 64 * 15 + 6, 100
     for pad in ((0, 0, 0), (1, 1, 3)):
         case = Case(oracle, "f64", ta, tb, m, n, k, -1.0, 1.0, pad=pad, seed=77)
-        run_and_check(cuda, mm, case, 3)
+        ref = case.reference()
+        for kid in (3, 4):
+            run_and_check(cuda, mm, case, kid, ref=ref)
 
 
 def test_dgemm_misaligned_base_pointers(cuda, mm, oracle):
@@ -83,7 +85,7 @@ def test_dgemm_misaligned_base_pointers(cuda, mm, oracle):
         devs.append((buf, off))
     dA, dB, dC = (b[o:o + h.size] for (b, o), h in zip(devs, (case.A, case.B, case.C)))
     assert dA.data_ptr() % 16 == 8 and dB.data_ptr() % 16 == 8
-    for kid in (2, 3):
+    for kid in (2, 3, 4):
         dC.copy_(torch.from_numpy(case.C.reshape(-1)))
         mm.gemm("f64", False, True, m, n, k, -1.0, dA, case.lda, dB, case.ldb, 1.0, dC, case.ldc, kid)
         torch.cuda.synchronize()
@@ -105,7 +107,7 @@ def test_dgemm_kernels_agree_on_a_larger_problem(cuda, mm, oracle):
     mm.fill("f64", A, m, k, m, mat=0)
     mm.fill("f64", B, n, k, n, mat=1)
     outs = {}
-    for kid in (0, 2, 3):
+    for kid in (0, 2, 3, 4):
         C = torch.empty(n * m, dtype=torch.float64, device="cuda")
         mm.fill("f64", C, m, n, m, mat=2)
         mm.gemm("f64", False, True, m, n, k, -1.0, A, m, B, n, 1.0, C, m, kid)
@@ -113,5 +115,5 @@ def test_dgemm_kernels_agree_on_a_larger_problem(cuda, mm, oracle):
         assert mm.device_status() == 0
         outs[kid] = C.cpu().numpy()
     scale = np.linalg.norm(outs[0])
-    for kid in (2, 3):
+    for kid in (2, 3, 4):
         assert np.linalg.norm(outs[kid] - outs[0]) / scale <= 1e-14, kid
