@@ -161,12 +161,25 @@ dgemm_dmma_ws_kernel(const double* __restrict__ A, const double* __restrict__ B,
         if (p.beta != 0.0 && kb == c_prefetch_kb) {
           // ask L2 for this tile's C lines: 64 columns of up to 1 KB, 16 columns per producer warp
           const uint32_t rows = p.m - m0 < (uint32_t)kWsBM ? p.m - m0 : (uint32_t)kWsBM;
-          for (uint32_t c = solo ? 0u : 16u * pw; c < (solo ? (uint32_t)kWsBN : 16u * pw + 16u); c += 16) {
-            const uint32_t col = n0 + c + (lane >> 1);
-            if (col < p.n) {
-              const double* c_col = C + (size_t)col * p.ldc + m0;
-              for (uint32_t r = (lane & 1) * 16; r < rows; r += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(c_col + r));
-              if (lane & 1) asm volatile("prefetch.global.L2 [%0];" ::"l"(c_col + rows - 1));
+          // (bulk prefetch, the 1-D form of the TMA prefetch, where the column pieces are 16-byte
+          // aligned: one request per column; otherwise one prefetch per 128-byte line)
+          const bool c_bulk = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) && (p.ldc & 1u) == 0 && (rows & 1u) == 0;
+          const uint32_t c_first = solo ? 0u : 16u * pw, c_last = solo ? (uint32_t)kWsBN : 16u * pw + 16u;
+          if (c_bulk) {
+            for (uint32_t c = c_first + lane; c < c_last; c += 32) {
+              const uint32_t col = n0 + c;
+              if (col < p.n)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(C + (size_t)col * p.ldc + m0), "r"(rows * 8u)
+                             : "memory");
+            }
+          } else {
+            for (uint32_t c = c_first; c < c_last; c += 16) {
+              const uint32_t col = n0 + c + (lane >> 1);
+              if (col < p.n) {
+                const double* c_col = C + (size_t)col * p.ldc + m0;
+                for (uint32_t r = (lane & 1) * 16; r < rows; r += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(c_col + r));
+                if (lane & 1) asm volatile("prefetch.global.L2 [%0];" ::"l"(c_col + rows - 1));
+              }
             }
           }
         }

@@ -132,12 +132,11 @@ def test_tuning_table_overrides_selection(mm, tmp_path):
     mm.tuning_clear()
 
 
-def test_fp64_selection_prefers_small_tiles_for_small_problems():
-    """No GPU needed: the choice depends on the tile count only (148 SMs assumed without a device)."""
+def test_fp64_selection_is_the_warp_specialised_tensor_kernel():
+    """No GPU needed."""
     import gemm_mmbo_b200 as mm
     BAD = 16
     mm.tuning_clear()
-    small = mm.select_kernel("f64", False, True, 1536, 2048, 384, BAD, 1536, BAD, 2048, BAD, 1536)
-    large = mm.select_kernel("f64", False, True, 44160, 2048, 384, BAD, 44160, BAD, 2048, BAD, 44160)
-    assert "MT064x064" in mm.kernel_name("f64", small) and "dmma_ws" in mm.kernel_name("f64", small)
-    assert "MT128x064" in mm.kernel_name("f64", large) and "dmma_ws" in mm.kernel_name("f64", large)
+    for m in (384, 1536, 44160):
+        kid = mm.select_kernel("f64", False, True, m, 2048, 384, BAD, m, BAD, 2048, BAD, 44160)
+        assert "dmma_ws_MT128x064" in mm.kernel_name("f64", kid)
