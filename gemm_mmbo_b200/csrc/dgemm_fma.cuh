@@ -22,6 +22,7 @@ struct DgemmParams {
   double alpha, beta;
   uint32_t wgm;
   uint32_t diag;  // diagnostic runs only (bit 0: no C traffic; results wrong by design), never set in production
+  uint32_t tma_a, tma_b;  // warp-specialised kernel: the operand is addressed through its tensor map
 };
 
 constexpr int kDgBM = 64, kDgBN = 64, kDgBK = 16, kDgThreads = 256;

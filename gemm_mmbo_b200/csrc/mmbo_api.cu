@@ -172,7 +172,8 @@ static EncodeTiledFn encode_fn() {
 // dimension 1 has `outer` elements `ld` elements apart.  128-byte swizzle; out-of-range
 // elements read as zero.
 static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem_bytes, const void* base,
-                       size_t inner, size_t outer, size_t ld, uint32_t box_inner, uint32_t box_outer) {
+                       size_t inner, size_t outer, size_t ld, uint32_t box_inner, uint32_t box_outer,
+                       CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return MMBO_ERR_NO_DRIVER_ENTRY;
   cuuint64_t dims[2] = {inner, outer};
@@ -180,7 +181,7 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem_byt
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? MMBO_OK : MMBO_ERR_TENSOR_MAP;
 }
@@ -664,6 +665,7 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
   p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
   p.alpha = alpha; p.beta = beta; p.wgm = env_u32("MMBO_WGM", kF64Rows[id].wgm);
   p.diag = env_u32("MMBO_DIAG", 0);
+  p.tma_a = p.tma_b = 0;
   if (id == 2) {  // fp64 tensor path
     const size_t gx2 = (g.m + kDmBM - 1) / kDmBM, gy2 = (g.n + kDmBN - 1) / kDmBN;
     if (gy2 > 65535) return MMBO_ERR_TOO_LARGE;
@@ -679,16 +681,38 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
     const size_t tiles = ((g.m + bm - 1) / bm) * ((g.n + kWsBN - 1) / kWsBN);
     if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
     const unsigned grid3 = (unsigned)std::min(tiles, (size_t)2 * (size_t)sm_count());  // two CTAs per SM
+    // An operand goes through TMA when its base is 16-byte aligned and its leading dimension even
+    // (strides in multiples of 16 bytes); the box is kWsPad elements wider than the tile along the
+    // contiguous index, which gives the slab its padded pitch.
+    CUtensorMap ta, tb;
+    p.tma_a = aligned16(g.A) && g.lda % 2 == 0;
+    p.tma_b = aligned16(g.B) && g.ldb % 2 == 0;
+    if (p.tma_a) {
+      const int rc = g.transA  // stored k x m (k contiguous) / m x k (m contiguous)
+          ? make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, g.A, g.k, g.m, g.lda, kWsBK + kWsPad, (uint32_t)bm, CU_TENSOR_MAP_SWIZZLE_NONE)
+          : make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, g.A, g.m, g.k, g.lda, (uint32_t)bm + kWsPad, kWsBK, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    } else {
+      memset(&ta, 0, sizeof(ta));
+    }
+    if (p.tma_b) {
+      const int rc = g.transB  // stored n x k (n contiguous) / k x n (k contiguous)
+          ? make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, g.B, g.n, g.k, g.ldb, kWsBN + kWsPad, kWsBK, CU_TENSOR_MAP_SWIZZLE_NONE)
+          : make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, g.B, g.k, g.n, g.ldb, kWsBK + kWsPad, kWsBN, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    } else {
+      memset(&tb, 0, sizeof(tb));
+    }
     auto launch = [&](auto kernel, size_t smem) -> int {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
-      kernel<<<grid3, kWsThreads, smem, st>>>(A, B, C, p);
+      kernel<<<grid3, kWsThreads, smem, st>>>(ta, tb, A, B, C, p);
       return (int)cudaGetLastError();
     };
-    auto by_tile = [&](auto ta, auto tb) -> int {
-      constexpr bool TA = decltype(ta)::value, TB = decltype(tb)::value;
-      if (id == 3) return launch(dgemm_dmma_ws_kernel<TA, TB, 128>, WsTile<128>::kSmemBytes);
-      return launch(dgemm_dmma_ws_kernel<TA, TB, 64>, WsTile<64>::kSmemBytes);
+    auto by_tile = [&](auto ta_, auto tb_) -> int {
+      constexpr bool TA = decltype(ta_)::value, TB = decltype(tb_)::value;
+      if (id == 3) return launch(dgemm_dmma_ws_kernel<TA, TB, 128>, WsTile<128, TA, !TB>::kSmemBytes);
+      return launch(dgemm_dmma_ws_kernel<TA, TB, 64>, WsTile<64, TA, !TB>::kSmemBytes);
     };
     using Yes = std::true_type;
     using No = std::false_type;
