@@ -640,11 +640,14 @@ static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
   return MMBO_ERR_BAD_KERNEL_ID;
 }
 
-// Default fp64 kernel: the warp-specialised tensor kernel with 128-row tiles.  The 64-row row
-// (id 4) measured slower at every size of the reference's sweep (19.9 against 24.4 TFLOP/s at
-// 1536 x 2048 x 384, equal at 384 x 2048 x 384): halving the tile halves the work per slab but not
-// the number of per-row bulk copies the producer issues for it.  It stays selectable.
-static int select_f64(const GemmArgs&) { return 3; }
+// Default fp64 kernel: the warp-specialised tensor kernel.  64-row tiles for short contractions
+// (the epilogue weighs more and more CTAs overlap it: 32.4 against 32.2 TFLOP/s at 44160 x 2048 x 384,
+// 31.8 / 30.1 at 11136, 17.2 / 14.7 at 384) and while 128-row tiles would not give every CTA slot
+// of the machine a tile (1024^3: 28.3 / 23.7); 128-row tiles otherwise (3072^3: 34.8 / 34.3).
+static int select_f64(const GemmArgs& g) {
+  const size_t tiles128 = ((g.m + 127) / 128) * ((g.n + kWsBN - 1) / kWsBN);
+  return (g.k <= 512 || tiles128 < 2 * (size_t)sm_count()) ? 4 : 3;
+}
 
 static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStream_t st) {
   if (g.m == 0 || g.n == 0) return MMBO_OK;

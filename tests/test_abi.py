@@ -133,10 +133,13 @@ def test_tuning_table_overrides_selection(mm, tmp_path):
 
 
 def test_fp64_selection_is_the_warp_specialised_tensor_kernel():
-    """No GPU needed."""
+    """No GPU needed (148 SMs assumed without a device): 64-row tiles for short contractions and
+    for problems with few tiles, 128-row tiles otherwise."""
     import gemm_mmbo_b200 as mm
     BAD = 16
     mm.tuning_clear()
-    for m in (384, 1536, 44160):
-        kid = mm.select_kernel("f64", False, True, m, 2048, 384, BAD, m, BAD, 2048, BAD, 44160)
-        assert "dmma_ws_MT128x064" in mm.kernel_name("f64", kid)
+    def name(m, n, k):
+        return mm.kernel_name("f64", mm.select_kernel("f64", False, True, m, n, k, BAD, m, BAD, n, BAD, m))
+    assert "dmma_ws_MT064x064" in name(44160, 2048, 384)
+    assert "dmma_ws_MT064x064" in name(1024, 1024, 1024)
+    assert "dmma_ws_MT128x064" in name(4096, 4096, 4096)
