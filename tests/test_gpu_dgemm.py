@@ -117,3 +117,16 @@ def test_dgemm_kernels_agree_on_a_larger_problem(cuda, mm, oracle):
     scale = np.linalg.norm(outs[0])
     for kid in (2, 3, 4):
         assert np.linalg.norm(outs[kid] - outs[0]) / scale <= 1e-14, kid
+
+
+@pytest.mark.parametrize("ta,tb", MODES)
+def test_dgemm_operand_feed_paths(cuda, mm, oracle, ta, tb):
+    """Each operand either goes through its tensor map (even leading dimension) or through
+    element copies (odd): all four combinations, both tile heights, ragged edges and a K tail."""
+    m, n, k = 330, 202, 90
+    for pad_a in (0, 1):
+        for pad_b in (0, 1):
+            case = Case(oracle, "f64", ta, tb, m, n, k, 1.5, -0.5, pad=(pad_a, pad_b, 1), seed=5 + 2 * pad_a + pad_b)
+            ref = case.reference()
+            for kid in (3, 4):
+                run_and_check(cuda, mm, case, kid, ref=ref)
