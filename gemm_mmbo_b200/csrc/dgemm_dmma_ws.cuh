@@ -62,9 +62,15 @@ struct WsTile {
   using SA = WsSlab<BM, A_KMAJOR>;
   using SB = WsSlab<kWsBN, B_KMAJOR>;
   static constexpr int kStageDoubles = SA::kDoubles + SB::kDoubles;
-  // two CTAs per SM: at most about 110 KB of ring each
-  static constexpr int kStages = (size_t)4 * kStageDoubles * 8 <= 110000 ? 4 : 3;
-  static constexpr size_t kSmemBytes = (size_t)kStages * kStageDoubles * sizeof(double) + 128;  // + slack to align the ring
+  // 64-row tiles leave room for the tile's old C, [col][BM + 4]: the producer brings it in with
+  // one TMA box well ahead of the epilogue that needs it, which then reads shared memory
+  // instead of waiting for HBM twice.
+  static constexpr bool kStageC = BM == 64;
+  static constexpr int kCPitch = BM + kWsPad;
+  static constexpr int kCDoubles = kStageC ? kWsBN * kCPitch : 0;
+  // two CTAs per SM: at most about 115 KB of dynamic shared memory each
+  static constexpr int kStages = ((size_t)4 * kStageDoubles + kCDoubles) * 8 + 128 <= 115000 ? 4 : 3;
+  static constexpr size_t kSmemBytes = ((size_t)kStages * kStageDoubles + kCDoubles) * sizeof(double) + 128;  // + slack to align the ring
   static constexpr int kFragM = BM / 16;  // m8 fragments per consumer warp (two warps along m)
 };
 // arrivals that complete a slab: one cp.async arrival per producer lane + the expect_tx arrival
@@ -122,7 +128,7 @@ __device__ __forceinline__ void ws_fill_elements(uint32_t slab, const double* __
 template <bool TRANS_A, bool TRANS_B, int BM>
 __global__ void __launch_bounds__(kWsThreads, 2)
 dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     const double* __restrict__ A, const double* __restrict__ B, double* __restrict__ C,
+                     const __grid_constant__ CUtensorMap tmap_c, const double* __restrict__ A, const double* __restrict__ B, double* __restrict__ C,
                      const DgemmParams p) {
   constexpr bool A_KMAJOR = TRANS_A, B_KMAJOR = !TRANS_B;  // which index is contiguous in memory
   using T = WsTile<BM, A_KMAJOR, B_KMAJOR>;
@@ -134,7 +140,10 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   // TMA writes whole boxes to 128-byte aligned shared memory
   double* const ws_smem = reinterpret_cast<double*>(ws_smem_raw + ((128u - (smem_u32(ws_smem_raw) & 127u)) & 127u));
   __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
+  __shared__ __align__(8) uint64_t c_full_bar, c_empty_bar;  // the staged C tile (64-row tiles, p.tma_c)
   __shared__ uint32_t abort_flag;
+  const bool stage_c = T::kStageC && p.tma_c && p.beta != 0.0;
+  double* const c_smem = ws_smem + kStages * T::kStageDoubles;  // [col][BM + 4]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t smem_a = smem_u32(ws_smem);
@@ -148,6 +157,8 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       mbar_init(smem_u32(&full_bar[s]), solo ? 33u : kWsFullCount);
       mbar_init(smem_u32(&empty_bar[s]), kWsConsumers);
     }
+    mbar_init(smem_u32(&c_full_bar), 1);
+    mbar_init(smem_u32(&c_empty_bar), kWsConsumers);
     fence_mbar_init();
   }
   __syncthreads();
@@ -164,15 +175,30 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (solo && pw != 0) return;
     // the epilogue's C lines are requested from L2 this many slabs before the tile's last one
     const uint32_t c_prefetch_kb = num_kb > 24u ? num_kb - 24u : 0u;
-    uint32_t issued = 0;
-    bool ok = true;
+    uint32_t issued = 0, c_phase = 0;
+    bool ok = true, c_in_flight = false;
+    // The staged C of a tile is requested a few slabs into the tile: by then the consumers are past
+    // the previous tile's epilogue, so the wait for the buffer does not hold up the slab ring.
+    const uint32_t c_stage_kb = num_kb > 4u ? 4u : num_kb - 1u;
     for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       uint32_t tile_m, tile_n;
       mmbo_tile_from_serial(tile, tiles_m, tiles_n, p.wgm, &tile_m, &tile_n);
       const uint32_t m0 = tile_m * BM, n0 = tile_n * kWsBN;
       const bool a_inside = m0 + BM <= p.m, b_inside = n0 + kWsBN <= p.n;
       for (uint32_t kb = 0; kb < num_kb; ++kb) {
-        if (p.beta != 0.0 && kb == c_prefetch_kb) {
+        if (stage_c && pw == 0 && kb == c_stage_kb) {
+          if (!mbar_wait(smem_u32(&c_empty_bar), c_phase ^ 1u, &abort_flag, kFaultWaitCLoad, 0)) {
+            ok = false;
+            break;
+          }
+          if (lane == 0) {
+            mbar_expect_tx(smem_u32(&c_full_bar), T::kCDoubles * 8u);
+            tma_load_2d(smem_u32(c_smem), &tmap_c, smem_u32(&c_full_bar), (int32_t)m0, (int32_t)n0);
+          }
+          c_in_flight = true;
+          c_phase ^= 1u;
+        }
+        if (p.beta != 0.0 && !stage_c && kb == c_prefetch_kb) {
           // Ask L2 for this tile's C: a bulk prefetch (the 1-D form of the TMA prefetch) per column
           // where the column pieces are 16-byte aligned, else one prefetch per 128-byte line.
           const uint32_t rows = p.m - m0 < (uint32_t)BM ? p.m - m0 : (uint32_t)BM;
@@ -230,6 +256,11 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       // Leave only after the copies in flight have landed: the element copies of this warp, and
       // the TMA boxes of the slabs issued last (a short bounded wait on their full barriers).
       ws_cp_async_wait_all();
+      if (c_in_flight && pw == 0) {  // the last staged C may still be landing
+        const uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(smem_u32(&c_full_bar), c_phase ^ 1u) && global_timer_ns() - t0 < MMBO_DRAIN_LIMIT_NS) {
+        }
+      }
       const uint32_t pending = issued < (uint32_t)kStages ? issued : (uint32_t)kStages;
       for (uint32_t i = 0; pw == 0 && i < pending; ++i) {
         stage = stage == 0 ? kStages - 1 : stage - 1;
@@ -247,6 +278,7 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int gid = lane >> 2, tig = lane & 3;                    // fragment coordinates of m8n8k4
   const int wm = (warp & 1) * (BM / 2), wn = (warp >> 1) * 32;  // this warp's (BM / 2) x 32 piece of the tile
   const double alpha = p.alpha, beta = p.beta;
+  uint32_t c_phase = 0;
   for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
     uint32_t tile_m, tile_n;
     mmbo_tile_from_serial(tile, tiles_m, tiles_n, p.wgm, &tile_m, &tile_n);
@@ -282,7 +314,28 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // accumulator (i, j): C[m = gid][n = 2*tig + {0, 1}] of the 8 x 8 block at (wm + 8i, wn + 8j).
     // C is read 32 values per thread at a time (four columns x eight row blocks, all loads of a
     // round before their first use) and the tile is done in two such rounds.
-    if ((p.diag & 1u) == 0u) {
+    if (stage_c) {
+      // old C from shared memory (element (row, col) of the tile at c_smem[col * kCPitch + row])
+      if (!mbar_wait(smem_u32(&c_full_bar), c_phase, &abort_flag, kFaultWaitCLoad, 1)) return;
+      c_phase ^= 1u;
+      const uint32_t row = m0 + wm + gid;
+      const uint32_t rows_left = p.m > row ? p.m - row : 0u;
+      const double* __restrict__ c_s = c_smem + wm + gid;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t cl = wn + 8 * j + 2 * tig + e, col = n0 + cl;
+          double* __restrict__ c_col = C + (size_t)col * p.ldc + row;
+#pragma unroll
+          for (int i = 0; i < kFragM; ++i) {
+            const double old = c_s[cl * T::kCPitch + 8 * i];
+            if (col < p.n && 8u * i < rows_left && (p.diag & 1u) == 0u) c_col[8 * i] = fma(beta, old, alpha * acc[i][j][e]);
+          }
+        }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&c_empty_bar));  // this warp has read its part of the staged tile
+    } else if ((p.diag & 1u) == 0u) {
       const uint32_t row = m0 + wm + gid;
       const uint32_t rows_left = p.m > row ? p.m - row : 0u;  // row block i is inside the matrix iff 8i < rows_left
 #pragma unroll

@@ -23,6 +23,7 @@ struct DgemmParams {
   uint32_t wgm;
   uint32_t diag;  // diagnostic runs only (bit 0: no C traffic; results wrong by design), never set in production
   uint32_t tma_a, tma_b;  // warp-specialised kernel: the operand is addressed through its tensor map
+  uint32_t tma_c;         // ... and the old C can be staged through shared memory (64-row tiles)
 };
 
 constexpr int kDgBM = 64, kDgBN = 64, kDgBK = 16, kDgThreads = 256;

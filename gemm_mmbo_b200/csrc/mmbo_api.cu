@@ -668,7 +668,7 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
   p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
   p.alpha = alpha; p.beta = beta; p.wgm = env_u32("MMBO_WGM", kF64Rows[id].wgm);
   p.diag = env_u32("MMBO_DIAG", 0);
-  p.tma_a = p.tma_b = 0;
+  p.tma_a = p.tma_b = p.tma_c = 0;
   if (id == 2) {  // fp64 tensor path
     const size_t gx2 = (g.m + kDmBM - 1) / kDmBM, gy2 = (g.n + kDmBN - 1) / kDmBN;
     if (gy2 > 65535) return MMBO_ERR_TOO_LARGE;
@@ -706,10 +706,20 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
     } else {
       memset(&tb, 0, sizeof(tb));
     }
+    // old C staged through shared memory (64-row tiles only): one box of 64 columns x (64 + 4) rows
+    CUtensorMap tc;
+    p.tma_c = id == 4 && beta != 0.0 && aligned16(g.C) && g.ldc % 2 == 0 && env_u32("MMBO_DGEMM_STAGE_C", 1) != 0;
+    if (p.tma_c) {
+      const int rc = make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, g.C, g.m, g.n, g.ldc, (uint32_t)bm + kWsPad, kWsBN,
+                                 CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    } else {
+      memset(&tc, 0, sizeof(tc));
+    }
     auto launch = [&](auto kernel, size_t smem) -> int {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
-      kernel<<<grid3, kWsThreads, smem, st>>>(ta, tb, A, B, C, p);
+      kernel<<<grid3, kWsThreads, smem, st>>>(ta, tb, tc, A, B, C, p);
       return (int)cudaGetLastError();
     };
     auto by_tile = [&](auto ta_, auto tb_) -> int {
