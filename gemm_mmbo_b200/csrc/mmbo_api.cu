@@ -17,6 +17,7 @@
 #include "../../include/mmbo_gemm.h"
 #include "dgemm_dmma.cuh"
 #include "dgemm_dmma_ws.cuh"
+#include "sgemm_ffma_ws.cuh"
 #include "dgemm_fma.cuh"
 #include "hgemm_tcgen05.cuh"
 #include "ref_kernels.cuh"
@@ -40,6 +41,7 @@ static const KernelRow kF32Rows[] = {
     {"sgemm_tf32x3_tcgen05_MT128x256x32_S4_CG2_WG192_WGM08", 128, 256, 192, 32, 4, 2, 8, 1},
     {"sgemm_tf32x3_tcgen05_MT128x128x32_S3_CG1_WG192_WGM08", 128, 128, 192, 32, 3, 1, 8, 1},
     {"sgemm_tf32x3_tcgen05_MT256x256x32_S3_CG2_WG384_WGM08", 256, 256, 384, 32, 3, 2, 8, 1},
+    {"sgemm_ffma_ws_MT128x128x16_S4_TT08_08_WG384_WGM08", 128, 128, 384, 16, 4, 1, 8, 0},
 };
 // fp16 rows: MT<tile m>x<tile n>x<DepthU>_S<stages>_CG<cta group>.
 static const KernelRow kF16Rows[] = {
@@ -224,6 +226,49 @@ static int launch_scale(const GemmArgs& g, cudaStream_t st) {
   dim3 grid((unsigned)gx, (unsigned)gy), block(32, 8);
   scale_c_kernel<T><<<grid, block, 0, st>>>(g.m, g.n, g.beta, static_cast<T*>(g.C), g.ldc);
   return (int)cudaGetLastError();
+}
+
+// FFMA kernel with a producer warpgroup: an operand goes through TMA when its tile rows are
+// contiguous in memory, its base 16-byte aligned and its leading dimension a multiple of 4.
+static int launch_sgemm_ffma_ws(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
+  SgemmParams p;
+  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
+  p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
+  p.alpha = g.alpha; p.beta = g.beta; p.wgm = wgm;
+  p.vec_a = p.vec_b = 0;
+  p.vec_c = aligned16(g.C) && g.ldc % 4 == 0;
+  SgemmWsFlags f;
+  f.tma_a = !g.transA && aligned16(g.A) && g.lda % 4 == 0;
+  f.tma_b = g.transB && aligned16(g.B) && g.ldb % 4 == 0;
+  CUtensorMap ta, tb;
+  memset(&ta, 0, sizeof(ta));
+  memset(&tb, 0, sizeof(tb));
+  if (f.tma_a) {
+    const int rc = make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.A, g.m, g.k, g.lda, kFwBM + kFwPad, kFwBK,
+                               CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+  }
+  if (f.tma_b) {
+    const int rc = make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.B, g.n, g.k, g.ldb, kFwBN + kFwPad, kFwBK,
+                               CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+  }
+  const size_t tiles = ((g.m + kFwBM - 1) / kFwBM) * ((g.n + kFwBN - 1) / kFwBN);
+  if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
+  const unsigned grid = (unsigned)std::min(tiles, (size_t)2 * (size_t)sm_count());
+  const float* A = static_cast<const float*>(g.A);
+  const float* B = static_cast<const float*>(g.B);
+  float* C = static_cast<float*>(g.C);
+  auto launch = [&](auto kernel) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    kernel<<<grid, kFwThreads, kFwSmemBytes, st>>>(ta, tb, A, B, C, p, f);
+    return (int)cudaGetLastError();
+  };
+  if (!g.transA && !g.transB) return launch(sgemm_ffma_ws_kernel<false, false>);
+  if (!g.transA && g.transB) return launch(sgemm_ffma_ws_kernel<false, true>);
+  if (g.transA && !g.transB) return launch(sgemm_ffma_ws_kernel<true, false>);
+  return launch(sgemm_ffma_ws_kernel<true, true>);
 }
 
 template <int BM, int BN, int TTM, int TTN>
@@ -588,6 +633,10 @@ static int select_f32(const GemmArgs& g) {
     return pair_tiles >= (uint64_t)(sm_count() / 2) ? 3 : 4;
   }
   const uint64_t big_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 127) / 128);
+  // The producer / consumer kernel walks tiles with a fixed stride: it wins once every CTA has
+  // many tiles (8192^3: 59.7 against 56.6 TFLOP/s), and loses while the last tiles of a launch
+  // leave CTAs alone on their SMs (4096^3: 52.4 against 55.5).
+  if (big_tiles >= 16ull * (uint64_t)sm_count()) return 6;
   return big_tiles >= 2ull * (uint64_t)sm_count() ? 1 : 2;
 }
 
@@ -626,6 +675,7 @@ static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
     case 0: return launch_simple<float>(g, st);
     case 1: return launch_sgemm_ffma<128, 128, 8, 8>(g, env_u32("MMBO_WGM", kF32Rows[1].wgm), st);
     case 2: return launch_sgemm_ffma<64, 64, 4, 4>(g, env_u32("MMBO_WGM", kF32Rows[2].wgm), st);
+    case 6: return launch_sgemm_ffma_ws(g, env_u32("MMBO_WGM", kF32Rows[6].wgm), st);
     case 3:
     case 4:
     case 5: {

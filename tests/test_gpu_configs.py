@@ -14,7 +14,7 @@ def test_config1_sgemm_nn_1024(cuda, mm, oracle):
     """SGEMM NN, M=N=K=1024, ld=1024, alpha=1, beta=0, A,B ~ U[-1,1), C = 0."""
     case = Case(oracle, "f32", False, False, 1024, 1024, 1024, 1.0, 0.0)
     case.C[:] = 0.0
-    for kid in (-1, 1, 2, 3, 4, 5):
+    for kid in (-1, 1, 2, 3, 4, 5, 6):
         run_and_check(cuda, mm, case, kid)
 
 
@@ -23,7 +23,7 @@ def test_config3_sgemm_ragged_padded(cuda, mm, oracle, ta, tb):
     """SGEMM, M=4095 N=4097 K=1023, every ld = extent + 3, alpha=1.5, beta=-0.25."""
     case = Case(oracle, "f32", ta, tb, 4095, 4097, 1023, 1.5, -0.25, pad=(3, 3, 3))
     ref = case.reference()
-    for kid in (-1, 1, 3, 5):
+    for kid in (-1, 1, 3, 5, 6):
         run_and_check(cuda, mm, case, kid, ref=ref)
 
 

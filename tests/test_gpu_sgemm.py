@@ -14,7 +14,7 @@ SHAPES = [(1, 1, 1), (5, 3, 2), (64, 64, 16), (65, 63, 17), (128, 128, 32), (129
           (200, 300, 100), (384, 256, 64), (257, 513, 129)]
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, 5, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, 5, 6, -1])
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_sgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
     for (m, n, k) in SHAPES:
@@ -23,13 +23,13 @@ def test_sgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
             run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, 5, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, 5, 6, -1])
 def test_sgemm_beta_zero_never_reads_c(cuda, mm, oracle, kernel_id):
     case = Case(oracle, "f32", False, True, 150, 70, 40, 2.0, 0.0, pad=(1, 2, 3), c_poison=True)
     run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, 5, -1])
+@pytest.mark.parametrize("kernel_id", [0, 1, 2, 3, 4, 5, 6, -1])
 def test_sgemm_k_zero_scales_c(cuda, mm, oracle, kernel_id):
     case = Case(oracle, "f32", False, False, 70, 33, 0, 2.0, 0.5, pad=(0, 0, 5))
     run_and_check(cuda, mm, case, kernel_id)
@@ -92,3 +92,13 @@ def test_sgemm_lent_workspace(cuda, mm, oracle):
     finally:
         mm.set_workspace(None)
     run_and_check(cuda, mm, case, 3)  # library-managed scratch again
+
+
+@pytest.mark.parametrize("ta,tb", MODES)
+def test_sgemm_producer_consumer_ffma_kernel(cuda, mm, oracle, ta, tb):
+    """fp32 id 6: more tiles than resident CTAs, ragged edges, a K tail; leading dimensions that
+    allow TMA (multiples of 4, for the operands whose tile rows are contiguous) and ones that do not."""
+    m, n, k = 128 * 20 + 12, 128 * 16 + 4, 100
+    for pad in ((0, 0, 0), (1, 3, 2)):
+        case = Case(oracle, "f32", ta, tb, m, n, k, 1.5, -0.25, pad=pad, seed=91)
+        run_and_check(cuda, mm, case, 6)
