@@ -143,3 +143,5 @@ def test_fp64_selection_is_the_warp_specialised_tensor_kernel():
     assert "dmma_ws_MT064x064" in name(44160, 2048, 384)
     assert "dmma_ws_MT064x064" in name(1024, 1024, 1024)
     assert "dmma_ws_MT128x064" in name(4096, 4096, 4096)
+    assert "dmma_ws_MT128x064" in name(2176, 2176, 2176)   # 578 tiles of 128 rows: 1.95 rounds of 296 slots
+    assert "dmma_ws_MT064x064" in name(2368, 2368, 2368)   # 703 tiles would be 2.4 rounds; 1369 of 64 rows are 4.6
