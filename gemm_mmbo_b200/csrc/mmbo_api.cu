@@ -255,7 +255,9 @@ static int launch_sgemm_ffma_ws(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   }
   const size_t tiles = ((g.m + kFwBM - 1) / kFwBM) * ((g.n + kFwBN - 1) / kFwBN);
   if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-  const unsigned grid = (unsigned)std::min(tiles, (size_t)2 * (size_t)sm_count());
+  // Eight CTAs per SM in the grid, two resident: as CTAs finish their few tiles the hardware starts the
+  // next ones, which balances the end of the launch (4096^3: 61.1 TFLOP/s against 52.3 with 2 per SM).
+  const unsigned grid = (unsigned)std::min(tiles, (size_t)8 * (size_t)sm_count());
   const float* A = static_cast<const float*>(g.A);
   const float* B = static_cast<const float*>(g.B);
   float* C = static_cast<float*>(g.C);
@@ -633,11 +635,9 @@ static int select_f32(const GemmArgs& g) {
     return pair_tiles >= (uint64_t)(sm_count() / 2) ? 3 : 4;
   }
   const uint64_t big_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 127) / 128);
-  // The producer / consumer kernel walks tiles with a fixed stride: it wins once every CTA has
-  // many tiles (8192^3: 59.7 against 56.6 TFLOP/s), and loses while the last tiles of a launch
-  // leave CTAs alone on their SMs (4096^3: 52.4 against 55.5).
-  if (big_tiles >= 16ull * (uint64_t)sm_count()) return 6;
-  return big_tiles >= 2ull * (uint64_t)sm_count() ? 1 : 2;
+  // The producer / consumer kernel from two tiles per SM on (2048^3: 51.0 against 45.8 TFLOP/s for id 1,
+  // 4096^3: 61.1 / 55.5, 8192^3: 61.4 / 56.6); the 64 x 64 kernel below that (1024^3: 30.6 against 23.0).
+  return big_tiles >= 2ull * (uint64_t)sm_count() ? 6 : 2;
 }
 
 static int select_f16(const GemmArgs& g) {
@@ -740,7 +740,7 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
     const size_t bm = id == 3 ? 128 : 64;
     const size_t tiles = ((g.m + bm - 1) / bm) * ((g.n + kWsBN - 1) / kWsBN);
     if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-    const unsigned grid3 = (unsigned)std::min(tiles, (size_t)2 * (size_t)sm_count());  // two CTAs per SM
+    const unsigned grid3 = (unsigned)std::min(tiles, (size_t)2 * (size_t)sm_count());  // two CTAs per SM (more made no difference)
     // An operand goes through TMA when its base is 16-byte aligned and its leading dimension even
     // (strides in multiples of 16 bytes); the box is kWsPad elements wider than the tile along the
     // contiguous index, which gives the slab its padded pitch.
