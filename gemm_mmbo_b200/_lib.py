@@ -27,6 +27,12 @@ SIGNATURES = {
     "mmbo_gemm_f16_bcast": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
                                            _fp, _vp, _sz, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
                                            ctypes.c_int, _vp]),
+    "mmbo_gemm_f16_mcast": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
+                                           _fp, _vp, _sz, _vp, ctypes.c_int, _vp]),
+    "mmbo_gemm_f16_sharded": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                             _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz, _fp, _vp, _sz, ctypes.c_int, _vp]),
+    "mmbo_gemm_f16_sharded_host": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int, ctypes.c_int, _sz, _sz,
+                                                  _sz, _fp, _vp, _sz, _vp, _sz, _fp, _vp, _sz, ctypes.c_int]),
     "mmbo_gemm_f64": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _dp, _vp, _sz, _vp, _sz,
                                      _dp, _vp, _sz, ctypes.c_int, _vp]),
     "mmbo_fill_f64": (ctypes.c_int, [_vp, _sz, _sz, _sz, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int,
@@ -59,6 +65,9 @@ SIGNATURES = {
     "mmbo_selftest_bounded_wait": (ctypes.c_int, [ctypes.c_ulonglong, _vp]),
     "mmbo_gemm_workspace_bytes": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _szp]),
     "mmbo_set_workspace": (ctypes.c_int, [_vp, _sz]),
+    "mmbo_set_option": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_uint]),
+    "mmbo_get_option": (ctypes.c_int, [ctypes.c_char_p, _u32p]),
+    "mmbo_launch_count": (ctypes.c_ulonglong, []),
     "mmbo_gemm_f32_noalloc": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
                                              _fp, _vp, _sz, _vp]),
 }

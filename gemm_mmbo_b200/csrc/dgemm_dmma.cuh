@@ -69,6 +69,9 @@ dgemm_dmma_kernel(const double* __restrict__ A, const double* __restrict__ B, do
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gid = lane >> 2, tig = lane & 3;      // fragment coordinates of m8n8k4
   const int wm = (warp & 3) * 32, wn = (warp >> 2) * 32;  // warp tile origin inside the block tile
+  A += (size_t)blockIdx.z * p.batch_a;  // problem blockIdx.z of a strided batch
+  B += (size_t)blockIdx.z * p.batch_b;
+  C += (size_t)blockIdx.z * p.batch_c;
 
   uint32_t tile_m, tile_n;
   mmbo_wgm_remap(blockIdx.x, blockIdx.y, gridDim.x, gridDim.y, p.wgm, &tile_m, &tile_n);

@@ -164,9 +164,16 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   __syncthreads();
 
   const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + kWsBN - 1) / kWsBN;
-  const uint32_t num_tiles = tiles_m * tiles_n;
+  const uint32_t tiles_per_problem = tiles_m * tiles_n;
+  const uint32_t num_tiles = tiles_per_problem * p.batch;  // strided batch: problem index slowest
   const uint32_t num_kb = (p.k + kWsBK - 1) / kWsBK;
   uint32_t stage = 0, phase = 0;
+  const bool batched = p.batch > 1u;  // 3-D tensor maps; single problems keep the 2-D forms
+  auto locate = [&](uint32_t tile, uint32_t* tm, uint32_t* tn) -> uint32_t {
+    const uint32_t prob = tile / tiles_per_problem;
+    mmbo_tile_from_serial(tile - prob * tiles_per_problem, tiles_m, tiles_n, p.wgm, tm, tn);
+    return prob;
+  };
 
   if (warp >= kWsConsumers) {
     // ----------------------------------------------------------------- producers ----
@@ -182,7 +189,7 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const uint32_t c_stage_kb = num_kb > 4u ? 4u : num_kb - 1u;
     for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       uint32_t tile_m, tile_n;
-      mmbo_tile_from_serial(tile, tiles_m, tiles_n, p.wgm, &tile_m, &tile_n);
+      const uint32_t prob = locate(tile, &tile_m, &tile_n);
       const uint32_t m0 = tile_m * BM, n0 = tile_n * kWsBN;
       const bool a_inside = m0 + BM <= p.m, b_inside = n0 + kWsBN <= p.n;
       for (uint32_t kb = 0; kb < num_kb; ++kb) {
@@ -193,7 +200,7 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
           if (lane == 0) {
             mbar_expect_tx(smem_u32(&c_full_bar), T::kCDoubles * 8u);
-            tma_load_2d(smem_u32(c_smem), &tmap_c, smem_u32(&c_full_bar), (int32_t)m0, (int32_t)n0);
+            tma_load_tile(batched, smem_u32(c_smem), &tmap_c, smem_u32(&c_full_bar), (int32_t)m0, (int32_t)n0, (int32_t)prob);
           }
           c_in_flight = true;
           c_phase ^= 1u;
@@ -202,20 +209,21 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           // Ask L2 for this tile's C: a bulk prefetch (the 1-D form of the TMA prefetch) per column
           // where the column pieces are 16-byte aligned, else one prefetch per 128-byte line.
           const uint32_t rows = p.m - m0 < (uint32_t)BM ? p.m - m0 : (uint32_t)BM;
-          const bool c_bulk = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) && (p.ldc & 1u) == 0 && (rows & 1u) == 0;
+          const double* __restrict__ Cp = C + (size_t)prob * p.batch_c;
+          const bool c_bulk = ((reinterpret_cast<uintptr_t>(Cp) & 15u) == 0) && (p.ldc & 1u) == 0 && (rows & 1u) == 0;
           const uint32_t c_first = solo ? 0u : 16u * pw, c_last = solo ? (uint32_t)kWsBN : 16u * pw + 16u;
           if (c_bulk) {
             for (uint32_t c = c_first + lane; c < c_last; c += 32) {
               const uint32_t col = n0 + c;
               if (col < p.n)
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(C + (size_t)col * p.ldc + m0), "r"(rows * 8u)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(Cp + (size_t)col * p.ldc + m0), "r"(rows * 8u)
                              : "memory");
             }
           } else {
             for (uint32_t c = c_first; c < c_last; c += 16) {
               const uint32_t col = n0 + c + (lane >> 1);
               if (col < p.n) {
-                const double* c_col = C + (size_t)col * p.ldc + m0;
+                const double* c_col = Cp + (size_t)col * p.ldc + m0;
                 for (uint32_t r = (lane & 1) * 16; r < rows; r += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(c_col + r));
                 if (lane & 1) asm volatile("prefetch.global.L2 [%0];" ::"l"(c_col + rows - 1));
               }
@@ -236,16 +244,18 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if (tx) mbar_expect_tx(full, tx);
           else mbar_arrive(full);
           // coordinates: (contiguous index, other index)
-          if (p.tma_a) tma_load_2d(slab_a, &tmap_a, full, A_KMAJOR ? (int32_t)l0 : (int32_t)m0, A_KMAJOR ? (int32_t)m0 : (int32_t)l0);
-          if (p.tma_b) tma_load_2d(slab_b, &tmap_b, full, B_KMAJOR ? (int32_t)l0 : (int32_t)n0, B_KMAJOR ? (int32_t)n0 : (int32_t)l0);
+          if (p.tma_a) tma_load_tile(batched, slab_a, &tmap_a, full, A_KMAJOR ? (int32_t)l0 : (int32_t)m0, A_KMAJOR ? (int32_t)m0 : (int32_t)l0, (int32_t)prob);
+          if (p.tma_b) tma_load_tile(batched, slab_b, &tmap_b, full, B_KMAJOR ? (int32_t)l0 : (int32_t)n0, B_KMAJOR ? (int32_t)n0 : (int32_t)l0, (int32_t)prob);
         }
         if (!p.tma_a) {
-          if (whole && a_inside) ws_fill_elements<BM, A_KMAJOR, false, kWsProducers>(slab_a, A, p.lda, m0, l0, p.m, p.k, lane, pw);
-          else ws_fill_elements<BM, A_KMAJOR, true, kWsProducers>(slab_a, A, p.lda, m0, l0, p.m, p.k, lane, pw);
+          const double* __restrict__ Ap = A + (size_t)prob * p.batch_a;
+          if (whole && a_inside) ws_fill_elements<BM, A_KMAJOR, false, kWsProducers>(slab_a, Ap, p.lda, m0, l0, p.m, p.k, lane, pw);
+          else ws_fill_elements<BM, A_KMAJOR, true, kWsProducers>(slab_a, Ap, p.lda, m0, l0, p.m, p.k, lane, pw);
         }
         if (!p.tma_b) {
-          if (whole && b_inside) ws_fill_elements<kWsBN, B_KMAJOR, false, kWsProducers>(slab_b, B, p.ldb, n0, l0, p.n, p.k, lane, pw);
-          else ws_fill_elements<kWsBN, B_KMAJOR, true, kWsProducers>(slab_b, B, p.ldb, n0, l0, p.n, p.k, lane, pw);
+          const double* __restrict__ Bp = B + (size_t)prob * p.batch_b;
+          if (whole && b_inside) ws_fill_elements<kWsBN, B_KMAJOR, false, kWsProducers>(slab_b, Bp, p.ldb, n0, l0, p.n, p.k, lane, pw);
+          else ws_fill_elements<kWsBN, B_KMAJOR, true, kWsProducers>(slab_b, Bp, p.ldb, n0, l0, p.n, p.k, lane, pw);
         }
         ws_cp_async_arrive(full);
         ++issued;
@@ -281,7 +291,8 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   uint32_t c_phase = 0;
   for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
     uint32_t tile_m, tile_n;
-    mmbo_tile_from_serial(tile, tiles_m, tiles_n, p.wgm, &tile_m, &tile_n);
+    const uint32_t prob = locate(tile, &tile_m, &tile_n);
+    double* __restrict__ Cp = C + (size_t)prob * p.batch_c;
     const uint32_t m0 = tile_m * BM, n0 = tile_n * kWsBN;
     double acc[kFragM][4][2];
 #pragma unroll
@@ -326,7 +337,7 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const uint32_t cl = wn + 8 * j + 2 * tig + e, col = n0 + cl;
-          double* __restrict__ c_col = C + (size_t)col * p.ldc + row;
+          double* __restrict__ c_col = Cp + (size_t)col * p.ldc + row;
 #pragma unroll
           for (int i = 0; i < kFragM; ++i) {
             const double old = c_s[cl * T::kCPitch + 8 * i];
@@ -347,7 +358,7 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (int q = 0; q < 4; ++q) {  // q = 2 * (j & 1) + e
           const uint32_t col = n0 + wn + 8 * (2 * jh + (q >> 1)) + 2 * tig + (q & 1);
           col_ok[q] = col < p.n;
-          c_col[q] = C + (size_t)col * p.ldc + row;
+          c_col[q] = Cp + (size_t)col * p.ldc + row;
         }
         if (beta != 0.0) {
 #pragma unroll

@@ -24,6 +24,10 @@ struct DgemmParams {
   uint32_t diag;  // diagnostic runs only (bit 0: no C traffic; results wrong by design), never set in production
   uint32_t tma_a, tma_b;  // warp-specialised kernel: the operand is addressed through its tensor map
   uint32_t tma_c;         // ... and the old C can be staged through shared memory (64-row tiles)
+  // strided batch (src/gemm/ref/Kernels.cpp:254 takes the problem index from the grid): number of
+  // problems and the elements between consecutive problems' A, B, C
+  uint32_t batch;
+  unsigned long long batch_a, batch_b, batch_c;
 };
 
 constexpr int kDgBM = 64, kDgBN = 64, kDgBK = 16, kDgThreads = 256;
@@ -70,6 +74,9 @@ dgemm_fma_kernel(const double* __restrict__ A, const double* __restrict__ B, dou
   __shared__ __align__(16) double sB[2][kDgBK * kPitch];
   const int tid = threadIdx.x;
   const int tx = tid % 16, ty = tid / 16;  // lanes run along m
+  A += (size_t)blockIdx.z * p.batch_a;  // problem blockIdx.z of a strided batch
+  B += (size_t)blockIdx.z * p.batch_b;
+  C += (size_t)blockIdx.z * p.batch_c;
 
   uint32_t tile_m, tile_n;
   mmbo_wgm_remap(blockIdx.x, blockIdx.y, gridDim.x, gridDim.y, p.wgm, &tile_m, &tile_n);

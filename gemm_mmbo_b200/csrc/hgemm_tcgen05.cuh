@@ -80,10 +80,16 @@ struct HgemmSmem {
 struct HgemmParams {
   uint32_t m, n, k;
   uint32_t tiles_m, tiles_n;  // ceil(m / TM), ceil(n / (128 * CG))
+  uint32_t batch;             // problems of a strided batch (the reference's kernel takes its batch index
+                              // from the grid: src/gemm/ref/Kernels.cpp:254); the persistent walk covers
+                              // batch * tiles_m * tiles_n tiles, problem index slowest
+  unsigned long long c_batch_stride;  // elements between the C of consecutive problems (plain epilogue)
   uint32_t wgm;               // work-group-mapping width (tile columns per block)
   float alpha, beta;
   __half* c;       // C and its leading dimension, for the epilogue without TMA
   uint32_t ldc;
+  __half* c_mc;    // optional: a multicast address of the same C window (every GPU bound to it receives each
+                   // store); when set, finished chunks are written there with multimem.st instead of the TMA store
   unsigned long long* trace;  // optional event trace (clock stamps of CTA 0), null in production
   uint32_t diag;   // diagnostic builds, results wrong by design (the reference keeps such
                    // kernels too: test_main_loop.s has no C store, error_kernel_000.s no waits):
@@ -158,8 +164,16 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
-  const uint32_t num_tiles = p.tiles_m * p.tiles_n;
+  const uint32_t tiles_per_problem = p.tiles_m * p.tiles_n;
+  const uint32_t num_tiles = tiles_per_problem * p.batch;
   const uint32_t num_kb = (p.k + kBlockK - 1) / kBlockK;
+  // tile id of the walk -> (tile row, tile column, problem of the batch)
+  const bool batched = p.batch > 1u;  // 3-D tensor maps; single problems keep the 2-D forms
+  auto locate = [&](uint32_t tile, uint32_t* tm, uint32_t* tn) -> uint32_t {
+    const uint32_t prob = tile / tiles_per_problem;
+    mmbo_tile_from_serial(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, p.wgm, tm, tn);
+    return prob;
+  };
 
   // ------------------------------------------------------------------ set-up --------
   if (threadIdx.x == 0) {
@@ -198,7 +212,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers) {
         uint32_t tm_idx, tn_idx;
-        mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
+        const int32_t prob = static_cast<int32_t>(locate(tile, &tm_idx, &tn_idx));
         // This CTA's share of the tile: its own 128 columns of C (rows of op(B)^T) and
         // its own TM / CG rows of op(A).
         const int32_t m0 = static_cast<int32_t>(tm_idx * TM + cta_rank * L::kAopRows);
@@ -215,8 +229,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
           if (cta_rank == 0) mbar_expect_tx(full_bar(stage), L::kStageBytes * CG);
           auto load = [&](uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1) {
-            if constexpr (CG == 2) tma_load_2d_pair(dst, map, bar, c0, c1);
-            else tma_load_2d(dst, map, bar, c0, c1);
+            if constexpr (CG == 2) tma_load_tile_pair(batched, dst, map, bar, c0, c1, prob);
+            else tma_load_tile(batched, dst, map, bar, c0, c1, prob);
           };
           if constexpr (B_KMAJOR) {
             load(s_bop, &tmap_b, k0, n0);  // box {64 k, 128 n}
@@ -334,7 +348,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t c_in_flight = 0;  // bit b: a load into buffer b of this warp has been requested and not yet awaited
     auto request_c = [&](uint32_t t, uint32_t set) {  // whole warp; lane 0 issues: chunks of tile t into buffer set `set`
       uint32_t tm, tn;
-      mmbo_tile_from_serial(t, p.tiles_m, p.tiles_n, p.wgm, &tm, &tn);
+      const int32_t pr = static_cast<int32_t>(locate(t, &tm, &tn));
       const uint32_t mr = tm * TM + col_base, nc = (tn * CG + cta_rank) * kTileN + 32u * q;
 #pragma unroll
       for (uint32_t c = 0; c < (kChunksPerWarp < 2u ? kChunksPerWarp : 2u); ++c) {
@@ -343,8 +357,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           c_in_flight |= 1u << (2u * set + c);
           if (lane == 0) {
             mbar_expect_tx(cload_bar(epi_w, 2u * set + c), kEpiBufBytes);
-            tma_load_2d(warp_buf_base + (2u * set + c) * kEpiBufBytes, &tmap_c, cload_bar(epi_w, 2u * set + c),
-                        static_cast<int32_t>(mrow0), static_cast<int32_t>(nc));
+            tma_load_tile(batched, warp_buf_base + (2u * set + c) * kEpiBufBytes, &tmap_c, cload_bar(epi_w, 2u * set + c),
+                        static_cast<int32_t>(mrow0), static_cast<int32_t>(nc), pr);
           }
         }
       }
@@ -352,7 +366,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (kCAhead && p.c_tma != 0u && use_c && walker < num_tiles) request_c(walker, 0u);
     for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers, ++local_tile) {
       uint32_t tm_idx, tn_idx;
-      mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
+      const int32_t prob = static_cast<int32_t>(locate(tile, &tm_idx, &tn_idx));
+      __half* const c_plain = p.c + static_cast<size_t>(prob) * p.c_batch_stride;  // this problem's C (plain epilogue)
       const uint32_t m0 = tm_idx * TM + col_base;
       const uint32_t ncol0 = (tn_idx * CG + cta_rank) * kTileN + 32u * q;  // first C column of this warp
       const uint32_t acc = local_tile & 1u;
@@ -377,12 +392,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // ahead, so that those requests will not have to go to HBM.
       if (!kCAhead && c_tma && use_c && lane == 0 && tile + num_walkers < num_tiles) {
         uint32_t nm, nn;
-        mmbo_tile_from_serial(tile + num_walkers, p.tiles_m, p.tiles_n, p.wgm, &nm, &nn);
+        const int32_t npr = static_cast<int32_t>(locate(tile + num_walkers, &nm, &nn));
         const uint32_t nm0 = nm * TM + col_base, nn0 = (nn * CG + cta_rank) * kTileN + 32u * q;
 #pragma unroll
         for (uint32_t c = 0; c < kChunksPerWarp; ++c)
           if (nm0 + 64u * c < p.m && nn0 < p.n)
-            tma_prefetch_l2_2d(&tmap_c, static_cast<int32_t>(nm0 + 64u * c), static_cast<int32_t>(nn0));
+            tma_prefetch_l2_tile(batched, &tmap_c, static_cast<int32_t>(nm0 + 64u * c), static_cast<int32_t>(nn0), npr);
       }
       // Every lane polls; the outcome is made warp-uniform so that the aligned
       // tcgen05 instructions below always run with a converged warp.
@@ -454,8 +469,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (load_c) c_in_flight |= 1u << (2u * set + b);
             if (load_c && lane == 0) {  // chunks beyond the two requested up front
               mbar_expect_tx(cload_bar(epi_w, 2u * set + b), kEpiBufBytes);
-              tma_load_2d(sbuf, &tmap_c, cload_bar(epi_w, 2u * set + b), static_cast<int32_t>(mrow0),
-                          static_cast<int32_t>(ncol0));
+              tma_load_tile(batched, sbuf, &tmap_c, cload_bar(epi_w, 2u * set + b), static_cast<int32_t>(mrow0),
+                          static_cast<int32_t>(ncol0), prob);
             }
           }
         } else {
@@ -470,7 +485,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               for (uint32_t hh = 0; hh < 2; ++hh) {
                 const uint32_t i = lane + 32u * hh, mi = mrow0 + i;
                 __half v = __float2half_rn(0.f);
-                if (mi < p.m && nj < p.n) v = p.c[(size_t)mi + (size_t)nj * p.ldc];
+                if (mi < p.m && nj < p.n) v = c_plain[(size_t)mi + (size_t)nj * p.ldc];
                 hb[t * 64u + ((((i >> 3) ^ (t & 7u)) << 3) | (i & 7u))] = v;
               }
             }
@@ -517,14 +532,30 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         if (tracer && c == 0) trace_stamp(p.trace, local_tile, 11);  // chunk 0 written to staging
-        if (c_tma) {
+        if (c_tma && p.c_mc != nullptr) {
+          // One store per 16-byte piece to the multicast address of C: NVSwitch delivers it to every GPU
+          // bound to that address, this one included, so the chunk crosses this GPU's links once however
+          // many GPUs receive it.  Eight lanes cover the 128 contiguous bytes of one column piece.
+          __syncwarp();
+          if (in_range && ok && (p.diag & 1u) == 0u) {
+#pragma unroll
+            for (uint32_t i = 0; i < 8; ++i) {
+              const uint32_t t = (lane >> 3) + 4u * i, j = lane & 7u;
+              const uint4 v = *reinterpret_cast<const uint4*>(gbuf + t * 128u + ((j ^ (t & 7u)) << 4));
+              const uint32_t row = mrow0 + 8u * j, col = ncol0 + t;
+              if (row < p.m && col < p.n) multimem_st_v4(p.c_mc + (size_t)row + (size_t)col * p.ldc, v);
+            }
+          }
+          fence_proxy_async_smem();  // the next writer of this buffer may be a TMA load of old C
+          __syncwarp();
+        } else if (c_tma) {
           fence_proxy_async_smem();
           __syncwarp();
           if (tracer && c == 0) trace_stamp(p.trace, local_tile, 12);  // fenced
           if (lane == 0) {
             if (in_range && ok && (p.diag & 1u) == 0u) {
-              tma_store_2d(&tmap_c, sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
-              for (uint32_t d = 0; d < peers.count; ++d)  // the same chunk into every peer's copy of C
+              tma_store_tile(batched, &tmap_c, sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0), prob);
+              for (uint32_t d = 0; d < peers.count; ++d)  // the same chunk into every peer's copy of C (single problems only)
                 tma_store_2d(&peers.map[d], sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
             }
             tma_store_commit();  // one group: the buffer is free again when all of them have read it
@@ -540,7 +571,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               for (uint32_t hh = 0; hh < 2; ++hh) {
                 const uint32_t i = lane + 32u * hh, mi = mrow0 + i;
                 const __half v = hb[t * 64u + ((((i >> 3) ^ (t & 7u)) << 3) | (i & 7u))];
-                if (mi < p.m && nj < p.n) p.c[(size_t)mi + (size_t)nj * p.ldc] = v;
+                if (mi < p.m && nj < p.n) c_plain[(size_t)mi + (size_t)nj * p.ldc] = v;
               }
             }
           }

@@ -20,6 +20,7 @@
 #include "sgemm_ffma_ws.cuh"
 #include "dgemm_fma.cuh"
 #include "hgemm_tcgen05.cuh"
+#include "nccl_dl.h"
 #include "ref_kernels.cuh"
 #include "sgemm_ffma.cuh"
 #include "sgemm_tf32x3.cuh"
@@ -117,6 +118,40 @@ static uint32_t env_u32(const char* name, uint32_t fallback) {
   return (uint32_t)strtoul(s, nullptr, 10);
 }
 
+// Switches for experiments and diagnosis.  The environment is read ONCE, when the first
+// call needs a setting; afterwards only mmbo_set_option changes them, so that a launch
+// costs no getenv scan and a production process cannot be flipped into a diagnostic
+// mode by an environment change after start-up.
+struct Settings {
+  uint32_t diag;           // MMBO_DIAG: diagnostic kernels, results wrong by design (bit 0 no C store, bit 1 no drain)
+  uint32_t wgm;            // MMBO_WGM: work-group-mapping width for every kernel; 0 = the table row's
+  uint32_t tf32_chunk;     // MMBO_TF32_CHUNK: stages per tensor-memory accumulation chain of the 3xTF32 kernels
+  uint32_t f32_exact;      // MMBO_F32_EXACT: automatic fp32 selection stays on the CUDA-core kernels
+  uint32_t dgemm_stage_c;  // MMBO_DGEMM_STAGE_C: 64-row fp64 tiles stage the old C through shared memory
+  uint32_t split_k;        // MMBO_SPLIT_K: 0 = automatic, 1 = never split, n > 1 = force n slices where a kernel can
+};
+static Settings load_settings() {
+  Settings s;
+  s.diag = env_u32("MMBO_DIAG", 0);
+  s.wgm = env_u32("MMBO_WGM", 0);
+  s.tf32_chunk = env_u32("MMBO_TF32_CHUNK", 4);
+  if (s.tf32_chunk == 0) s.tf32_chunk = 1;
+  s.f32_exact = env_u32("MMBO_F32_EXACT", 0);
+  s.dgemm_stage_c = env_u32("MMBO_DGEMM_STAGE_C", 1);
+  s.split_k = env_u32("MMBO_SPLIT_K", 0);
+  return s;
+}
+static Settings& settings() {
+  static Settings s = load_settings();
+  return s;
+}
+static uint32_t wgm_of(const KernelRow& row) { return settings().wgm ? settings().wgm : (uint32_t)row.wgm; }
+
+// Kernel launches queued by this library since it was loaded (every <<<>>> and
+// cudaLaunchKernelEx of a GEMM, split or scale kernel; not the operand generator).
+static unsigned long long g_launch_count = 0;
+#define MMBO_COUNT_LAUNCH() (++g_launch_count)
+
 // ------------------------------------------------------------------ validation -------
 struct GemmArgs {
   int transA, transB;
@@ -128,6 +163,10 @@ struct GemmArgs {
   // fp16 tensor-core kernels only: further copies of the C window (peer GPUs) the epilogue stores to
   void* const* peers = nullptr;
   int npeers = 0;
+  // ... or one multicast address of the same window (NVSwitch replicates each store to every GPU bound to it)
+  void* c_multicast = nullptr;
+  // strided batch: `batch` problems whose operands are sA / sB / sC elements apart
+  size_t batch = 1, sA = 0, sB = 0, sC = 0;
 };
 
 static int validate(const GemmArgs& g, const float* alpha, const float* beta) {
@@ -170,9 +209,27 @@ static EncodeTiledFn encode_fn() {
   return g_encode;
 }
 
-// 2-D map over a column-major array: dimension 0 (contiguous) has `inner` elements,
-// dimension 1 has `outer` elements `ld` elements apart.  128-byte swizzle; out-of-range
-// elements read as zero.
+// Map over a column-major array (or a strided batch of them): dimension 0 (contiguous) has
+// `inner` elements, dimension 1 has `outer` elements `ld` elements apart and, for a batch, dimension 2
+// has `nbatch` problems `batch_stride` elements apart.  128-byte swizzle by default; out-of-range elements read as zero.
+static int make_map(CUtensorMap* map, CUtensorMapDataType dt, size_t elem_bytes, const void* base,
+                    size_t inner, size_t outer, size_t ld, uint32_t box_inner, uint32_t box_outer,
+                    CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, size_t nbatch = 1,
+                    size_t batch_stride = 0) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return MMBO_ERR_NO_DRIVER_ENTRY;
+  cuuint64_t dims[3] = {inner, outer, nbatch};
+  cuuint64_t strides[2] = {ld * elem_bytes, batch_stride * elem_bytes};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  // a single problem is a 2-D map (the kernels then use the 2-D instruction forms)
+  CUresult r = enc(map, dt, nbatch > 1 ? 3 : 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MMBO_OK : MMBO_ERR_TENSOR_MAP;
+}
+
+// Plain 2-D map (the peer copies of C, which the epilogue addresses with two coordinates).
 static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem_bytes, const void* base,
                        size_t inner, size_t outer, size_t ld, uint32_t box_inner, uint32_t box_outer,
                        CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
@@ -186,6 +243,13 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem_byt
                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? MMBO_OK : MMBO_ERR_TENSOR_MAP;
+}
+
+// A batch stride TMA can take: a multiple of 16 bytes below 2^40 (a single problem has none).
+static bool batch_stride_ok(size_t batch, size_t stride_elems, size_t elem_bytes) {
+  if (batch <= 1) return true;
+  const unsigned long long b = (unsigned long long)stride_elems * elem_bytes;
+  return stride_elems != 0 && b % 16 == 0 && b < (1ull << 40);
 }
 
 // Self-test of the bounded-wait machinery: one thread waits on a barrier that nothing
@@ -210,21 +274,23 @@ constexpr size_t kTraceWords = 64 * 16;
 template <typename T>
 static int launch_simple(const GemmArgs& g, cudaStream_t st) {
   const size_t gx = (g.m + 31) / 32, gy = (g.n + 7) / 8;
-  if (gy > 65535 || gx > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-  dim3 grid((unsigned)gx, (unsigned)gy), block(32, 8);
+  if (gy > 65535 || gx > 0x7fffffffull || g.batch > 65535) return MMBO_ERR_TOO_LARGE;
+  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch), block(32, 8);
   gemm_simple_kernel<T><<<grid, block, 0, st>>>(g.transA, g.transB, g.m, g.n, g.k, g.alpha,
                                                 static_cast<const T*>(g.A), g.lda,
                                                 static_cast<const T*>(g.B), g.ldb, g.beta,
-                                                static_cast<T*>(g.C), g.ldc);
+                                                static_cast<T*>(g.C), g.ldc, g.sA, g.sB, g.sC);
+  MMBO_COUNT_LAUNCH();
   return (int)cudaGetLastError();
 }
 
 template <typename T>
 static int launch_scale(const GemmArgs& g, cudaStream_t st) {
   const size_t gx = (g.m + 31) / 32, gy = (g.n + 7) / 8;
-  if (gy > 65535 || gx > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-  dim3 grid((unsigned)gx, (unsigned)gy), block(32, 8);
-  scale_c_kernel<T><<<grid, block, 0, st>>>(g.m, g.n, g.beta, static_cast<T*>(g.C), g.ldc);
+  if (gy > 65535 || gx > 0x7fffffffull || g.batch > 65535) return MMBO_ERR_TOO_LARGE;
+  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch), block(32, 8);
+  scale_c_kernel<T><<<grid, block, 0, st>>>(g.m, g.n, g.beta, static_cast<T*>(g.C), g.ldc, g.sC);
+  MMBO_COUNT_LAUNCH();
   return (int)cudaGetLastError();
 }
 
@@ -235,6 +301,7 @@ static int launch_sgemm_ffma_ws(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
   p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
   p.alpha = g.alpha; p.beta = g.beta; p.wgm = wgm;
+  p.batch_a = p.batch_b = p.batch_c = 0;
   p.vec_a = p.vec_b = 0;
   p.vec_c = aligned16(g.C) && g.ldc % 4 == 0;
   SgemmWsFlags f;
@@ -265,6 +332,7 @@ static int launch_sgemm_ffma_ws(const GemmArgs& g, uint32_t wgm, cudaStream_t st
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwSmemBytes);
     if (e != cudaSuccess) return (int)e;
     kernel<<<grid, kFwThreads, kFwSmemBytes, st>>>(ta, tb, A, B, C, p, f);
+    MMBO_COUNT_LAUNCH();
     return (int)cudaGetLastError();
   };
   if (!g.transA && !g.transB) return launch(sgemm_ffma_ws_kernel<false, false>);
@@ -280,15 +348,17 @@ static int launch_sgemm_ffma(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
   p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
   p.alpha = g.alpha; p.beta = g.beta; p.wgm = wgm;
+  p.batch_a = g.sA; p.batch_b = g.sB; p.batch_c = g.sC;
   // 128-bit accesses: base and pitch 16-byte aligned, and the contiguous extent a
-  // multiple of 4 so that no vector straddles the matrix edge.
+  // multiple of 4 so that no vector straddles the matrix edge (every problem of a batch).
+  const bool batched = g.batch > 1;
   const size_t a_contig = g.transA ? g.k : g.m, b_contig = g.transB ? g.n : g.k;
-  p.vec_a = aligned16(g.A) && g.lda % 4 == 0 && a_contig % 4 == 0;
-  p.vec_b = aligned16(g.B) && g.ldb % 4 == 0 && b_contig % 4 == 0;
-  p.vec_c = aligned16(g.C) && g.ldc % 4 == 0;
+  p.vec_a = aligned16(g.A) && g.lda % 4 == 0 && a_contig % 4 == 0 && (!batched || g.sA % 4 == 0);
+  p.vec_b = aligned16(g.B) && g.ldb % 4 == 0 && b_contig % 4 == 0 && (!batched || g.sB % 4 == 0);
+  p.vec_c = aligned16(g.C) && g.ldc % 4 == 0 && (!batched || g.sC % 4 == 0);
   const size_t gx = (g.m + BM - 1) / BM, gy = (g.n + BN - 1) / BN;
-  if (gy > 65535) return MMBO_ERR_TOO_LARGE;
-  dim3 grid((unsigned)gx, (unsigned)gy), block((BM / TTM) * (BN / TTN));
+  if (gy > 65535 || g.batch > 65535) return MMBO_ERR_TOO_LARGE;
+  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch), block((BM / TTM) * (BN / TTN));
   const float* A = static_cast<const float*>(g.A);
   const float* B = static_cast<const float*>(g.B);
   float* C = static_cast<float*>(g.C);
@@ -300,6 +370,7 @@ static int launch_sgemm_ffma(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
     sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, true, false><<<grid, block, 0, st>>>(A, B, C, p);
   else
     sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, true, true><<<grid, block, 0, st>>>(A, B, C, p);
+  MMBO_COUNT_LAUNCH();
   return (int)cudaGetLastError();
 }
 
@@ -350,6 +421,7 @@ static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
+  MMBO_COUNT_LAUNCH();
   return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p, peers);
 }
 
@@ -357,22 +429,24 @@ template <int TM, int STAGES, int CG, int EW = 4>
 static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
   CUtensorMap ta, tb, tc;
   int rc;
+  constexpr auto F16 = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  constexpr auto SW = CU_TENSOR_MAP_SWIZZLE_128B;
   // op(A): K-major when transposed (stored k x m), MN-major otherwise (stored m x k).
   if (g.transA)
-    rc = make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.k, g.m, g.lda, kBlockK, TM / CG);
+    rc = make_map(&ta, F16, 2, g.A, g.k, g.m, g.lda, kBlockK, TM / CG, SW, g.batch, g.sA);
   else
-    rc = make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.A, g.m, g.k, g.lda, 64, kBlockK);
+    rc = make_map(&ta, F16, 2, g.A, g.m, g.k, g.lda, 64, kBlockK, SW, g.batch, g.sA);
   if (rc) return rc;
   // op(B): K-major when not transposed (stored k x n), MN-major otherwise (stored n x k).
   if (!g.transB)
-    rc = make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.B, g.k, g.n, g.ldb, kBlockK, kTileN);
+    rc = make_map(&tb, F16, 2, g.B, g.k, g.n, g.ldb, kBlockK, kTileN, SW, g.batch, g.sB);
   else
-    rc = make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.B, g.n, g.k, g.ldb, 64, kBlockK);
+    rc = make_map(&tb, F16, 2, g.B, g.n, g.k, g.ldb, 64, kBlockK, SW, g.batch, g.sB);
   if (rc) return rc;
   // C through TMA only when whole 16-byte units stay inside the matrix (see HgemmParams).
-  const bool c_tma = aligned16(g.C) && g.ldc % 8 == 0 && g.m % 8 == 0;
+  const bool c_tma = aligned16(g.C) && g.ldc % 8 == 0 && g.m % 8 == 0 && batch_stride_ok(g.batch, g.sC, 2);
   if (c_tma) {
-    rc = make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.C, g.m, g.n, g.ldc, 64, 32);
+    rc = make_map(&tc, F16, 2, g.C, g.m, g.n, g.ldc, 64, 32, SW, g.batch, g.sC);
     if (rc) return rc;
   } else {
     tc = ta;  // placeholder, never dereferenced by the plain epilogue
@@ -380,10 +454,11 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   static HgemmPeerMaps peers;  // (callers hold the library lock)
   peers.count = 0;
   if (g.npeers > 0) {
-    if (!c_tma || g.npeers > kMaxPeerCopies) return MMBO_ERR_KERNEL_UNSUITABLE;  // peer copies go through TMA stores only
+    // peer copies go through TMA stores only, and only for a single problem
+    if (!c_tma || g.npeers > kMaxPeerCopies || g.batch != 1) return MMBO_ERR_KERNEL_UNSUITABLE;
     for (int d = 0; d < g.npeers; ++d) {
       if (!g.peers[d] || !aligned16(g.peers[d])) return MMBO_ERR_KERNEL_UNSUITABLE;
-      rc = make_map_2d(&peers.map[d], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.peers[d], g.m, g.n, g.ldc, 64, 32);
+      rc = make_map_2d(&peers.map[d], F16, 2, g.peers[d], g.m, g.n, g.ldc, 64, 32);
       if (rc) return rc;
     }
     peers.count = (uint32_t)g.npeers;
@@ -393,12 +468,20 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
   p.tiles_m = (uint32_t)((g.m + TM - 1) / TM);
   p.tiles_n = (uint32_t)((g.n + kTileN * CG - 1) / (kTileN * CG));
+  p.batch = (uint32_t)g.batch;
+  p.c_batch_stride = g.sC;
   p.wgm = wgm;
   p.alpha = g.alpha; p.beta = g.beta;
   p.c = static_cast<__half*>(g.C); p.ldc = (uint32_t)g.ldc; p.c_tma = c_tma ? 1u : 0u;
+  p.c_mc = nullptr;
+  if (g.c_multicast) {
+    // the multicast window is written with 16-byte stores of whole column pieces
+    if (!c_tma || g.batch != 1 || !aligned16(g.c_multicast) || g.npeers > 0) return MMBO_ERR_KERNEL_UNSUITABLE;
+    p.c_mc = static_cast<__half*>(g.c_multicast);
+  }
   p.trace = g_trace_buffer;  // null unless mmbo_debug_trace armed it
-  p.diag = env_u32("MMBO_DIAG", 0);  // diagnostic builds (no C store / no drain): never set in production
-  const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
+  p.diag = settings().diag;  // diagnostic builds (no C store / no drain): never set in production
+  const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n * g.batch;
   if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
   if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, true>(ta, tb, tc, p, peers, tiles, st);
   if (g.transA && g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, false>(ta, tb, tc, p, peers, tiles, st);
@@ -407,14 +490,20 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
 }
 
 // ------------------------------------------------------------------ scratch memory --
-// One scratch buffer per device, used by the kernels that repack operands (the
-// 3xTF32 SGEMM).  Either the caller lends one (mmbo_set_workspace) or the library grows
-// its own on demand.  Calls that use scratch and overlap on the GPU (different streams)
-// would race on it: such callers lend a buffer per stream and serialise per buffer.
+// One scratch buffer per device, used by the kernels that repack operands (the 3xTF32
+// SGEMM, fp16 operands TMA cannot address, split-K partial sums).  Either the caller lends
+// one (mmbo_set_workspace) or the library grows its own on demand.  Calls that use it are
+// ordered on the GPU by the library itself: every user records an event behind its last
+// kernel, and the next user on a DIFFERENT stream first makes its stream wait for that
+// event, so that two streams never work in the buffer at the same time (the reference's
+// kernels use no scratch, so a caller coming from it has no reason to expect a hazard).
 struct Workspace {
   void* ptr;
   size_t bytes;
   bool user;
+  cudaEvent_t last_use;      // recorded behind the last kernel that used the buffer
+  cudaStream_t last_stream;  // stream of that kernel
+  bool used;
 };
 static Workspace g_ws[kMaxDevices];
 
@@ -428,6 +517,7 @@ static int ensure_workspace(size_t bytes, void** out) {
       cudaError_t e = cudaFree(w.ptr);  // waits for the kernels still using it
       w.ptr = nullptr;
       w.bytes = 0;
+      w.used = false;
       if (e != cudaSuccess) return (int)e;
     }
     cudaError_t e = cudaMalloc(&w.ptr, bytes);
@@ -441,17 +531,44 @@ static int ensure_workspace(size_t bytes, void** out) {
   return MMBO_OK;
 }
 
+// Called before the first kernel of a call that uses the scratch buffer ...
+static int workspace_acquire(cudaStream_t st) {
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
+  Workspace& w = g_ws[dev];
+  if (w.used && w.last_stream != st) {
+    cudaError_t e = cudaStreamWaitEvent(st, w.last_use, 0);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return MMBO_OK;
+}
+// ... and behind its last one.
+static int workspace_release(cudaStream_t st) {
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
+  Workspace& w = g_ws[dev];
+  if (!w.last_use) {
+    cudaError_t e = cudaEventCreateWithFlags(&w.last_use, cudaEventDisableTiming);
+    if (e != cudaSuccess) return (int)e;
+  }
+  cudaError_t e = cudaEventRecord(w.last_use, st);
+  if (e != cudaSuccess) return (int)e;
+  w.last_stream = st;
+  w.used = true;
+  return MMBO_OK;
+}
+
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Scratch layout of the 3xTF32 SGEMM: A_hi, A_lo (m rows of Kpad floats), B_hi, B_lo (n rows).
+// Scratch layout of the 3xTF32 SGEMM: A_hi, A_lo (batch x m rows of Kpad floats), B_hi, B_lo (batch x n rows).
 struct Tf32Scratch {
   size_t kpad, a_bytes, b_bytes, total;
 };
-static Tf32Scratch tf32_scratch(size_t m, size_t n, size_t k) {
+static Tf32Scratch tf32_scratch(size_t m, size_t n, size_t k, size_t batch = 1) {
   Tf32Scratch s;
   s.kpad = align_up(k, 32);
-  s.a_bytes = align_up(m * s.kpad * 4, 1024);
-  s.b_bytes = align_up(n * s.kpad * 4, 1024);
+  s.a_bytes = align_up(batch * m * s.kpad * 4, 1024);
+  s.b_bytes = align_up(batch * n * s.kpad * 4, 1024);
   s.total = 2 * (s.a_bytes + s.b_bytes);
   return s;
 }
@@ -463,15 +580,18 @@ static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float*
   auto kern = sgemm_tf32x3_kernel<TM, STAGES, CG, EW>;
   CUtensorMap ta_hi, ta_lo, tb_hi, tb_lo, tc;
   int rc;
-  if ((rc = make_map_2d(&ta_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a_hi, g.k, g.m, kpad, kTfBlockK, TM / CG))) return rc;
-  if ((rc = make_map_2d(&ta_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a_lo, g.k, g.m, kpad, kTfBlockK, TM / CG))) return rc;
-  if ((rc = make_map_2d(&tb_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b_hi, g.k, g.n, kpad, kTfBlockK, kTfTileN))) return rc;
-  if ((rc = make_map_2d(&tb_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b_lo, g.k, g.n, kpad, kTfBlockK, kTfTileN))) return rc;
+  constexpr auto F32 = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  constexpr auto SW = CU_TENSOR_MAP_SWIZZLE_128B;
+  // packed operands of problem b start b * rows * kpad floats into their array
+  if ((rc = make_map(&ta_hi, F32, 4, a_hi, g.k, g.m, kpad, kTfBlockK, TM / CG, SW, g.batch, g.m * kpad))) return rc;
+  if ((rc = make_map(&ta_lo, F32, 4, a_lo, g.k, g.m, kpad, kTfBlockK, TM / CG, SW, g.batch, g.m * kpad))) return rc;
+  if ((rc = make_map(&tb_hi, F32, 4, b_hi, g.k, g.n, kpad, kTfBlockK, kTfTileN, SW, g.batch, g.n * kpad))) return rc;
+  if ((rc = make_map(&tb_lo, F32, 4, b_lo, g.k, g.n, kpad, kTfBlockK, kTfTileN, SW, g.batch, g.n * kpad))) return rc;
   // TMA stores whole 16-byte units: only when m is a multiple of 4 floats do they stay
   // inside the matrix.
-  const bool c_tma = aligned16(g.C) && g.ldc % 4 == 0 && g.m % 4 == 0;
+  const bool c_tma = aligned16(g.C) && g.ldc % 4 == 0 && g.m % 4 == 0 && batch_stride_ok(g.batch, g.sC, 4);
   if (c_tma) {
-    if ((rc = make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.C, g.m, g.n, g.ldc, 32, 32))) return rc;
+    if ((rc = make_map(&tc, F32, 4, g.C, g.m, g.n, g.ldc, 32, 32, SW, g.batch, g.sC))) return rc;
   } else {
     tc = ta_hi;  // placeholder, never dereferenced by the plain epilogue
   }
@@ -479,11 +599,12 @@ static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float*
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
   p.tiles_m = (uint32_t)((g.m + TM - 1) / TM);
   p.tiles_n = (uint32_t)((g.n + kTfTileN * CG - 1) / (kTfTileN * CG));
+  p.batch = (uint32_t)g.batch;
+  p.c_batch_stride = g.sC;
   p.wgm = wgm; p.alpha = g.alpha; p.beta = g.beta;
   p.c = static_cast<float*>(g.C); p.ldc = (uint32_t)g.ldc; p.c_tma = c_tma ? 1u : 0u;
-  p.chunk = env_u32("MMBO_TF32_CHUNK", 4);
-  if (p.chunk == 0) p.chunk = 1;
-  const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n;
+  p.chunk = settings().tf32_chunk;
+  const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n * g.batch;
   if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
 
   static bool attr_done[kMaxDevices] = {};
@@ -520,30 +641,33 @@ static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float*
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
+  MMBO_COUNT_LAUNCH();
   return (int)cudaLaunchKernelEx(&cfg, kern, ta_hi, ta_lo, tb_hi, tb_lo, tc, p);
 }
 
 // Split + repack of both operands into `scratch`, then the tensor-core GEMM.
 template <int TM, int STAGES, int CG, int EW = 4>
 static int run_tf32x3(const GemmArgs& g, void* scratch, uint32_t wgm, cudaStream_t st) {
-  const Tf32Scratch s = tf32_scratch(g.m, g.n, g.k);
-  if (((g.m + 63) / 64) > 65535 || ((g.n + 63) / 64) > 65535) return MMBO_ERR_TOO_LARGE;
+  const Tf32Scratch s = tf32_scratch(g.m, g.n, g.k, g.batch);
+  if (((g.m + 63) / 64) > 65535 || ((g.n + 63) / 64) > 65535 || g.batch > 65535) return MMBO_ERR_TOO_LARGE;
   char* base = static_cast<char*>(scratch);
   float* a_hi = reinterpret_cast<float*>(base);
   float* a_lo = reinterpret_cast<float*>(base + s.a_bytes);
   float* b_hi = reinterpret_cast<float*>(base + 2 * s.a_bytes);
   float* b_lo = reinterpret_cast<float*>(base + 2 * s.a_bytes + s.b_bytes);
   const dim3 block(256);
-  const dim3 grid_a((unsigned)((g.k + 63) / 64), (unsigned)((g.m + 63) / 64));
-  const dim3 grid_b((unsigned)((g.k + 63) / 64), (unsigned)((g.n + 63) / 64));
+  const dim3 grid_a((unsigned)((g.k + 63) / 64), (unsigned)((g.m + 63) / 64), (unsigned)g.batch);
+  const dim3 grid_b((unsigned)((g.k + 63) / 64), (unsigned)((g.n + 63) / 64), (unsigned)g.batch);
   const float* A = static_cast<const float*>(g.A);
   const float* B = static_cast<const float*>(g.B);
   // op(A)(i,l): row index contiguous unless transposed; op(B)(l,j) as an n x k operand:
   // row index contiguous when transposed.
-  if (!g.transA) split_pack_kernel<true><<<grid_a, block, 0, st>>>(A, g.lda, (uint32_t)g.m, (uint32_t)g.k, (uint32_t)s.kpad, a_hi, a_lo);
-  else split_pack_kernel<false><<<grid_a, block, 0, st>>>(A, g.lda, (uint32_t)g.m, (uint32_t)g.k, (uint32_t)s.kpad, a_hi, a_lo);
-  if (g.transB) split_pack_kernel<true><<<grid_b, block, 0, st>>>(B, g.ldb, (uint32_t)g.n, (uint32_t)g.k, (uint32_t)s.kpad, b_hi, b_lo);
-  else split_pack_kernel<false><<<grid_b, block, 0, st>>>(B, g.ldb, (uint32_t)g.n, (uint32_t)g.k, (uint32_t)s.kpad, b_hi, b_lo);
+  if (!g.transA) split_pack_kernel<true><<<grid_a, block, 0, st>>>(A, g.lda, (uint32_t)g.m, (uint32_t)g.k, (uint32_t)s.kpad, a_hi, a_lo, g.sA);
+  else split_pack_kernel<false><<<grid_a, block, 0, st>>>(A, g.lda, (uint32_t)g.m, (uint32_t)g.k, (uint32_t)s.kpad, a_hi, a_lo, g.sA);
+  MMBO_COUNT_LAUNCH();
+  if (g.transB) split_pack_kernel<true><<<grid_b, block, 0, st>>>(B, g.ldb, (uint32_t)g.n, (uint32_t)g.k, (uint32_t)s.kpad, b_hi, b_lo, g.sB);
+  else split_pack_kernel<false><<<grid_b, block, 0, st>>>(B, g.ldb, (uint32_t)g.n, (uint32_t)g.k, (uint32_t)s.kpad, b_hi, b_lo, g.sB);
+  MMBO_COUNT_LAUNCH();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   return launch_tf32x3_gemm<TM, STAGES, CG, EW>(g, a_hi, a_lo, b_hi, b_lo, s.kpad, wgm, st);
@@ -620,24 +744,32 @@ static int tune_lookup(int dtype, const GemmArgs& g) {
 }
 
 // ------------------------------------------------------------------ selection --------
+// Exact fp32 (CUDA-core FFMA) choice: the producer / consumer kernel from two tiles per SM on
+// (2048^3: 51.0 against 45.8 TFLOP/s for id 1, 4096^3: 61.1 / 55.5, 8192^3: 61.4 / 56.6); the
+// 64 x 64 kernel below that (1024^3: 30.6 against 23.0).
+static int select_f32_exact(const GemmArgs& g) {
+  const uint64_t big_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 127) / 128) * g.batch;
+  return big_tiles >= 2ull * (uint64_t)sm_count() ? 6 : 2;
+}
+
 static int select_f32(const GemmArgs& g) {
   if (g.k == 0) return 0;
+  const bool exact = settings().f32_exact != 0;
   const int tuned = tune_lookup(MMBO_DTYPE_F32, g);
-  if (tuned >= 0) return tuned;
+  // A tuned row that names a split-precision tensor-core kernel is ignored when the caller asked
+  // for exact fp32 arithmetic: the switch is a statement about numerics, the table one about speed.
+  if (tuned >= 0 && !(exact && kF32Rows[tuned].tensor)) return tuned;
   // The split-precision tensor-core kernels hold the fp32 tolerance and are several
   // times faster than the FFMA pipe once the three launches they need are amortised.
   // MMBO_F32_EXACT=1 keeps automatic selection on the CUDA-core kernels.
-  const double work = (double)g.m * (double)g.n * (double)g.k;
-  if (work >= 512.0 * 512.0 * 512.0 && env_u32("MMBO_F32_EXACT", 0) == 0) {
-    const uint64_t big_pairs = (uint64_t)((g.m + 255) / 256) * ((g.n + 255) / 256);
+  const double work = (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
+  if (work >= 512.0 * 512.0 * 512.0 && !exact) {
+    const uint64_t big_pairs = (uint64_t)((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch;
     if (big_pairs >= 2ull * (uint64_t)(sm_count() / 2)) return 5;  // 256 x 256 tiles, two waves or more
-    const uint64_t pair_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 255) / 256);
+    const uint64_t pair_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 255) / 256) * g.batch;
     return pair_tiles >= (uint64_t)(sm_count() / 2) ? 3 : 4;
   }
-  const uint64_t big_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 127) / 128);
-  // The producer / consumer kernel from two tiles per SM on (2048^3: 51.0 against 45.8 TFLOP/s for id 1,
-  // 4096^3: 61.1 / 55.5, 8192^3: 61.4 / 56.6); the 64 x 64 kernel below that (1024^3: 30.6 against 23.0).
-  return big_tiles >= 2ull * (uint64_t)sm_count() ? 6 : 2;
+  return select_f32_exact(g);
 }
 
 static int select_f16(const GemmArgs& g) {
@@ -647,6 +779,7 @@ static int select_f16(const GemmArgs& g) {
   // Operands TMA cannot address are realigned through scratch first; that only pays off
   // once the product dwarfs the copies.
   if (!hgemm_tma_ok(g) && (double)g.m * (double)g.n * (double)g.k < 256.0 * 256.0 * 256.0) return 0;
+  const uint64_t nb = g.batch;  // every problem of a strided batch adds its tiles to the walk
   // Score = fraction of the machine kept busy over whole waves of tiles x relative
   // speed of the kernel on a full wave (measured on 8192^3).
   const double sms = (double)sm_count();
@@ -654,11 +787,11 @@ static int select_f16(const GemmArgs& g) {
     const double waves = (double)((tiles + (uint64_t)walkers - 1) / (uint64_t)walkers);
     return (double)tiles / (waves * walkers);
   };
-  const uint64_t t1 = (uint64_t)((g.m + 255) / 256) * ((g.n + 127) / 128);
-  const uint64_t t2 = (uint64_t)((g.m + 127) / 128) * ((g.n + 127) / 128);
-  const uint64_t t3 = (uint64_t)((g.m + 255) / 256) * ((g.n + 255) / 256);
+  const uint64_t t1 = nb * ((g.m + 255) / 256) * ((g.n + 127) / 128);
+  const uint64_t t2 = nb * ((g.m + 127) / 128) * ((g.n + 127) / 128);
+  const uint64_t t3 = nb * ((g.m + 255) / 256) * ((g.n + 255) / 256);
   // useful fraction of each tile (ragged edges waste tensor work)
-  auto fill = [&](uint64_t tiles, double tm, double tn) { return ((double)g.m * (double)g.n) / ((double)tiles * tm * tn); };
+  auto fill = [&](uint64_t tiles, double tm, double tn) { return ((double)nb * (double)g.m * (double)g.n) / ((double)tiles * tm * tn); };
   const double s1 = 0.80 * eff(t1, sms) * fill(t1, 256, 128);
   const double s2 = 0.70 * eff(t2, sms) * fill(t2, 128, 128);
   const double s3 = 1.00 * eff(t3, sms / 2) * fill(t3, 256, 256);
@@ -668,23 +801,38 @@ static int select_f16(const GemmArgs& g) {
   return s1 >= s2 ? 1 : 2;
 }
 
+// Automatic selection for a call that is about to run: a split-precision row whose scratch
+// does not fit the buffer the caller lent falls back to the CUDA-core kernels instead of failing.
+static int select_f32_fitting(const GemmArgs& g) {
+  const int id = select_f32(g);
+  if (id >= 3 && id <= 5) {
+    const int dev = current_device();
+    if (dev >= 0 && dev < kMaxDevices && g_ws[dev].user && g_ws[dev].bytes < tf32_scratch(g.m, g.n, g.k, g.batch).total)
+      return select_f32_exact(g);
+  }
+  return id;
+}
+
 static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
   if (g.m == 0 || g.n == 0) return MMBO_OK;
   if (g.k == 0) return launch_scale<float>(g, st);
   switch (id) {
     case 0: return launch_simple<float>(g, st);
-    case 1: return launch_sgemm_ffma<128, 128, 8, 8>(g, env_u32("MMBO_WGM", kF32Rows[1].wgm), st);
-    case 2: return launch_sgemm_ffma<64, 64, 4, 4>(g, env_u32("MMBO_WGM", kF32Rows[2].wgm), st);
-    case 6: return launch_sgemm_ffma_ws(g, env_u32("MMBO_WGM", kF32Rows[6].wgm), st);
+    case 1: return launch_sgemm_ffma<128, 128, 8, 8>(g, wgm_of(kF32Rows[1]), st);
+    case 2: return launch_sgemm_ffma<64, 64, 4, 4>(g, wgm_of(kF32Rows[2]), st);
+    case 6: return launch_sgemm_ffma_ws(g, wgm_of(kF32Rows[6]), st);
     case 3:
     case 4:
     case 5: {
       void* scratch = nullptr;
-      const int rc = ensure_workspace(tf32_scratch(g.m, g.n, g.k).total, &scratch);
+      int rc = ensure_workspace(tf32_scratch(g.m, g.n, g.k, g.batch).total, &scratch);
       if (rc) return rc;
-      if (id == 3) return run_tf32x3<128, 4, 2>(g, scratch, env_u32("MMBO_WGM", kF32Rows[3].wgm), st);
-      if (id == 5) return run_tf32x3<256, 3, 2, 8>(g, scratch, env_u32("MMBO_WGM", kF32Rows[5].wgm), st);
-      return run_tf32x3<128, 3, 1>(g, scratch, env_u32("MMBO_WGM", kF32Rows[4].wgm), st);
+      if ((rc = workspace_acquire(st))) return rc;
+      if (id == 3) rc = run_tf32x3<128, 4, 2>(g, scratch, wgm_of(kF32Rows[3]), st);
+      else if (id == 5) rc = run_tf32x3<256, 3, 2, 8>(g, scratch, wgm_of(kF32Rows[5]), st);
+      else rc = run_tf32x3<128, 3, 1>(g, scratch, wgm_of(kF32Rows[4]), st);
+      const int rc2 = workspace_release(st);
+      return rc ? rc : rc2;
     }
   }
   return MMBO_ERR_BAD_KERNEL_ID;
@@ -696,8 +844,8 @@ static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
 // of the machine a tile (1024^3: 28.3 / 23.7); 128-row tiles otherwise (3072^3: 34.8 / 34.3).
 static int select_f64(const GemmArgs& g) {
   const size_t slots = 2 * (size_t)sm_count();  // CTAs resident at once
-  const size_t tiles128 = ((g.m + 127) / 128) * ((g.n + kWsBN - 1) / kWsBN);
-  const size_t tiles64 = ((g.m + 63) / 64) * ((g.n + kWsBN - 1) / kWsBN);
+  const size_t tiles128 = g.batch * ((g.m + 127) / 128) * ((g.n + kWsBN - 1) / kWsBN);
+  const size_t tiles64 = g.batch * ((g.m + 63) / 64) * ((g.n + kWsBN - 1) / kWsBN);
   if (g.k <= 512 || tiles128 < slots) return 4;
   // Longer contractions: the tile height whose tile count fills whole rounds of CTA slots better
   // (2368^3 with 128-row tiles: 703 tiles = 2.4 rounds, 27.4 TFLOP/s against 34.4 at 2176^3 = 1.95
@@ -711,64 +859,72 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
   const double* A = static_cast<const double*>(g.A);
   const double* B = static_cast<const double*>(g.B);
   double* C = static_cast<double*>(g.C);
+  if (g.batch > 65535) return MMBO_ERR_TOO_LARGE;
   if (g.k == 0 || id == 0) {
     const size_t gx = (g.m + 31) / 32, gy = (g.n + 7) / 8;
     if (gy > 65535 || gx > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-    dim3 grid((unsigned)gx, (unsigned)gy), block(32, 8);
-    if (g.k == 0) scale_c_f64_kernel<<<grid, block, 0, st>>>(g.m, g.n, beta, C, g.ldc);
-    else gemm_simple_f64_kernel<<<grid, block, 0, st>>>(g.transA, g.transB, g.m, g.n, g.k, alpha, A, g.lda, B, g.ldb, beta, C, g.ldc);
+    dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch), block(32, 8);
+    if (g.k == 0) scale_c_f64_kernel<<<grid, block, 0, st>>>(g.m, g.n, beta, C, g.ldc, g.sC);
+    else gemm_simple_f64_kernel<<<grid, block, 0, st>>>(g.transA, g.transB, g.m, g.n, g.k, alpha, A, g.lda, B, g.ldb, beta, C, g.ldc,
+                                                         g.sA, g.sB, g.sC);
+    MMBO_COUNT_LAUNCH();
     return (int)cudaGetLastError();
   }
   if (id < 1 || id > 4) return MMBO_ERR_BAD_KERNEL_ID;
   DgemmParams p;
   p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
   p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
-  p.alpha = alpha; p.beta = beta; p.wgm = env_u32("MMBO_WGM", kF64Rows[id].wgm);
-  p.diag = env_u32("MMBO_DIAG", 0);
+  p.alpha = alpha; p.beta = beta; p.wgm = wgm_of(kF64Rows[id]);
+  p.diag = settings().diag;
   p.tma_a = p.tma_b = p.tma_c = 0;
+  p.batch = (uint32_t)g.batch;
+  p.batch_a = g.sA; p.batch_b = g.sB; p.batch_c = g.sC;
   if (id == 2) {  // fp64 tensor path
     const size_t gx2 = (g.m + kDmBM - 1) / kDmBM, gy2 = (g.n + kDmBN - 1) / kDmBN;
     if (gy2 > 65535) return MMBO_ERR_TOO_LARGE;
-    dim3 grid2((unsigned)gx2, (unsigned)gy2);
+    dim3 grid2((unsigned)gx2, (unsigned)gy2, (unsigned)g.batch);
     if (!g.transA && !g.transB) dgemm_dmma_kernel<false, false><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
     else if (!g.transA && g.transB) dgemm_dmma_kernel<false, true><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
     else if (g.transA && !g.transB) dgemm_dmma_kernel<true, false><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
     else dgemm_dmma_kernel<true, true><<<grid2, kDmThreads, 0, st>>>(A, B, C, p);
+    MMBO_COUNT_LAUNCH();
     return (int)cudaGetLastError();
   }
   if (id == 3 || id == 4) {  // fp64 tensor path, producer and consumer warpgroups, persistent; 128- or 64-row tiles
     const size_t bm = id == 3 ? 128 : 64;
-    const size_t tiles = ((g.m + bm - 1) / bm) * ((g.n + kWsBN - 1) / kWsBN);
+    const size_t tiles = ((g.m + bm - 1) / bm) * ((g.n + kWsBN - 1) / kWsBN) * g.batch;
     if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
     const unsigned grid3 = (unsigned)std::min(tiles, (size_t)2 * (size_t)sm_count());  // two CTAs per SM (more made no difference)
     // An operand goes through TMA when its base is 16-byte aligned and its leading dimension even
     // (strides in multiples of 16 bytes); the box is kWsPad elements wider than the tile along the
     // contiguous index, which gives the slab its padded pitch.
     CUtensorMap ta, tb;
-    p.tma_a = aligned16(g.A) && g.lda % 2 == 0;
-    p.tma_b = aligned16(g.B) && g.ldb % 2 == 0;
+    constexpr auto F64 = CU_TENSOR_MAP_DATA_TYPE_FLOAT64;
+    constexpr auto NOSW = CU_TENSOR_MAP_SWIZZLE_NONE;
+    p.tma_a = aligned16(g.A) && g.lda % 2 == 0 && batch_stride_ok(g.batch, g.sA, 8);
+    p.tma_b = aligned16(g.B) && g.ldb % 2 == 0 && batch_stride_ok(g.batch, g.sB, 8);
     if (p.tma_a) {
       const int rc = g.transA  // stored k x m (k contiguous) / m x k (m contiguous)
-          ? make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, g.A, g.k, g.m, g.lda, kWsBK + kWsPad, (uint32_t)bm, CU_TENSOR_MAP_SWIZZLE_NONE)
-          : make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, g.A, g.m, g.k, g.lda, (uint32_t)bm + kWsPad, kWsBK, CU_TENSOR_MAP_SWIZZLE_NONE);
+          ? make_map(&ta, F64, 8, g.A, g.k, g.m, g.lda, kWsBK + kWsPad, (uint32_t)bm, NOSW, g.batch, g.sA)
+          : make_map(&ta, F64, 8, g.A, g.m, g.k, g.lda, (uint32_t)bm + kWsPad, kWsBK, NOSW, g.batch, g.sA);
       if (rc) return rc;
     } else {
       memset(&ta, 0, sizeof(ta));
     }
     if (p.tma_b) {
       const int rc = g.transB  // stored n x k (n contiguous) / k x n (k contiguous)
-          ? make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, g.B, g.n, g.k, g.ldb, kWsBN + kWsPad, kWsBK, CU_TENSOR_MAP_SWIZZLE_NONE)
-          : make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, g.B, g.k, g.n, g.ldb, kWsBK + kWsPad, kWsBN, CU_TENSOR_MAP_SWIZZLE_NONE);
+          ? make_map(&tb, F64, 8, g.B, g.n, g.k, g.ldb, kWsBN + kWsPad, kWsBK, NOSW, g.batch, g.sB)
+          : make_map(&tb, F64, 8, g.B, g.k, g.n, g.ldb, kWsBK + kWsPad, kWsBN, NOSW, g.batch, g.sB);
       if (rc) return rc;
     } else {
       memset(&tb, 0, sizeof(tb));
     }
     // old C staged through shared memory (64-row tiles only): one box of 64 columns x (64 + 4) rows
     CUtensorMap tc;
-    p.tma_c = id == 4 && beta != 0.0 && aligned16(g.C) && g.ldc % 2 == 0 && env_u32("MMBO_DGEMM_STAGE_C", 1) != 0;
+    p.tma_c = id == 4 && beta != 0.0 && aligned16(g.C) && g.ldc % 2 == 0 && settings().dgemm_stage_c != 0 &&
+              batch_stride_ok(g.batch, g.sC, 8);
     if (p.tma_c) {
-      const int rc = make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, g.C, g.m, g.n, g.ldc, (uint32_t)bm + kWsPad, kWsBN,
-                                 CU_TENSOR_MAP_SWIZZLE_NONE);
+      const int rc = make_map(&tc, F64, 8, g.C, g.m, g.n, g.ldc, (uint32_t)bm + kWsPad, kWsBN, NOSW, g.batch, g.sC);
       if (rc) return rc;
     } else {
       memset(&tc, 0, sizeof(tc));
@@ -777,6 +933,7 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
       kernel<<<grid3, kWsThreads, smem, st>>>(ta, tb, tc, A, B, C, p);
+      MMBO_COUNT_LAUNCH();
       return (int)cudaGetLastError();
     };
     auto by_tile = [&](auto ta_, auto tb_) -> int {
@@ -793,11 +950,12 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
   }
   const size_t gx = (g.m + kDgBM - 1) / kDgBM, gy = (g.n + kDgBN - 1) / kDgBN;
   if (gy > 65535) return MMBO_ERR_TOO_LARGE;
-  dim3 grid((unsigned)gx, (unsigned)gy);
+  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch);
   if (!g.transA && !g.transB) dgemm_fma_kernel<false, false><<<grid, kDgThreads, 0, st>>>(A, B, C, p);
   else if (!g.transA && g.transB) dgemm_fma_kernel<false, true><<<grid, kDgThreads, 0, st>>>(A, B, C, p);
   else if (g.transA && !g.transB) dgemm_fma_kernel<true, false><<<grid, kDgThreads, 0, st>>>(A, B, C, p);
   else dgemm_fma_kernel<true, true><<<grid, kDgThreads, 0, st>>>(A, B, C, p);
+  MMBO_COUNT_LAUNCH();
   return (int)cudaGetLastError();
 }
 
@@ -805,8 +963,9 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
 // multiple of 8) are first copied, column by column, into scratch with an aligned pitch
 // (a strided device-to-device copy, no arithmetic), then the tensor-core kernel runs on
 // the copies.  C needs no copy: the epilogue without TMA handles any C.
-static int realign_f16(GemmArgs& g, cudaStream_t st) {
+static int realign_f16(GemmArgs& g, cudaStream_t st, bool* scratch_used) {
   const bool a_ok = aligned16(g.A) && g.lda % 8 == 0, b_ok = aligned16(g.B) && g.ldb % 8 == 0;
+  *scratch_used = false;
   if (a_ok && b_ok) return MMBO_OK;
   const size_t rowsA = g.transA ? g.k : g.m, colsA = g.transA ? g.m : g.k;
   const size_t rowsB = g.transB ? g.n : g.k, colsB = g.transB ? g.k : g.n;
@@ -816,6 +975,8 @@ static int realign_f16(GemmArgs& g, cudaStream_t st) {
   void* scratch = nullptr;
   int rc = ensure_workspace(a_bytes + b_bytes, &scratch);
   if (rc) return rc;
+  if ((rc = workspace_acquire(st))) return rc;
+  *scratch_used = true;
   char* base = static_cast<char*>(scratch);
   cudaError_t e;
   if (!a_ok) {
@@ -839,15 +1000,21 @@ static int run_f16(const GemmArgs& g_in, int id, cudaStream_t st) {
   if (id == 0) return launch_simple<__half>(g_in, st);
   if (id < 0 || id >= kNumF16) return MMBO_ERR_BAD_KERNEL_ID;
   GemmArgs g = g_in;
-  const int rc = realign_f16(g, st);
+  bool scratch_used = false;
+  int rc = realign_f16(g, st, &scratch_used);
   if (rc) return rc;
   switch (id) {
-    case 1: return launch_hgemm_tcgen05<256, 4, 1>(g, env_u32("MMBO_WGM", kF16Rows[1].wgm), st);
-    case 2: return launch_hgemm_tcgen05<128, 6, 1>(g, env_u32("MMBO_WGM", kF16Rows[2].wgm), st);
-    case 3: return launch_hgemm_tcgen05<256, 6, 2>(g, env_u32("MMBO_WGM", kF16Rows[3].wgm), st);
-    case 4: return launch_hgemm_tcgen05<256, 3, 2, 8>(g, env_u32("MMBO_WGM", kF16Rows[4].wgm), st);
+    case 1: rc = launch_hgemm_tcgen05<256, 4, 1>(g, wgm_of(kF16Rows[1]), st); break;
+    case 2: rc = launch_hgemm_tcgen05<128, 6, 1>(g, wgm_of(kF16Rows[2]), st); break;
+    case 3: rc = launch_hgemm_tcgen05<256, 6, 2>(g, wgm_of(kF16Rows[3]), st); break;
+    case 4: rc = launch_hgemm_tcgen05<256, 3, 2, 8>(g, wgm_of(kF16Rows[4]), st); break;
+    default: rc = MMBO_ERR_BAD_KERNEL_ID;
   }
-  return MMBO_ERR_BAD_KERNEL_ID;
+  if (scratch_used) {
+    const int rc2 = workspace_release(st);
+    if (!rc) rc = rc2;
+  }
+  return rc;
 }
 
 // ------------------------------------------------------------------ host operands ----
@@ -858,8 +1025,8 @@ static int run_f16(const GemmArgs& g_in, int id, cudaStream_t st) {
 // j+1, the GEMM of panel j and the copy-out of panel j-1 overlap on three streams.
 struct HostPipe {
   bool ready;
-  cudaStream_t s_in, s_mm, s_out;
-  cudaEvent_t ev_a, ev_in[2], ev_mm[2], ev_out[2];
+  cudaStream_t s_in, s_mm, s_out, s_cc;  // copy in, GEMM, copy out, collectives (sharded A)
+  cudaEvent_t ev_a, ev_cc, ev_in[2], ev_mm[2], ev_out[2];
   void* buf;
   size_t bytes;
 };
@@ -871,7 +1038,9 @@ static int pipe_setup(HostPipe& hp, size_t bytes) {
     if ((e = cudaStreamCreateWithFlags(&hp.s_in, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
     if ((e = cudaStreamCreateWithFlags(&hp.s_mm, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
     if ((e = cudaStreamCreateWithFlags(&hp.s_out, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
+    if ((e = cudaStreamCreateWithFlags(&hp.s_cc, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
     cudaEventCreateWithFlags(&hp.ev_a, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&hp.ev_cc, cudaEventDisableTiming);
     for (int i = 0; i < 2; ++i) {
       cudaEventCreateWithFlags(&hp.ev_in[i], cudaEventDisableTiming);
       cudaEventCreateWithFlags(&hp.ev_mm[i], cudaEventDisableTiming);
@@ -889,7 +1058,55 @@ static int pipe_setup(HostPipe& hp, size_t bytes) {
   return MMBO_OK;
 }
 
-static int gemm_host(int dtype, const GemmArgs& h, int kernelId, double alpha64 = 0.0, double beta64 = 0.0) {
+// A replicated over the GPUs of a node without every rank pushing all of it through the host
+// bridge: rank r copies only its share of A's stored columns host -> device, then the shares
+// are exchanged over NVLink (ncclAllGather in place when the shares are equal, one grouped
+// ncclBroadcast per rank otherwise).
+struct ShardedA {
+  int n_gpus, rank;
+  void* comm;  // ncclComm_t of the caller
+};
+
+static int stage_a_sharded(const ShardedA& sa, HostPipe& hp, const GemmArgs& h, size_t es, char* dA, size_t dlda,
+                           size_t rowsA, size_t colsA) {
+  NcclApi& nc = nccl_api();
+  if (!nc.ok()) return MMBO_ERR_NO_NCCL;
+  const size_t al = 16 / es;  // shares start on 16-byte boundaries of the compact device layout
+  size_t c0 = 0, cn = 0;
+  int rc = mmbo_shard_columns(colsA, sa.n_gpus, sa.rank, al, &c0, &cn);
+  if (rc) return rc;
+  cudaError_t e;
+  if (cn > 0) {
+    e = cudaMemcpy2DAsync(dA + c0 * dlda * es, dlda * es, static_cast<const char*>(h.A) + c0 * h.lda * es, h.lda * es,
+                          rowsA * es, cn, cudaMemcpyHostToDevice, hp.s_in);
+    if (e != cudaSuccess) return (int)e;
+  }
+  cudaEventRecord(hp.ev_a, hp.s_in);
+  cudaStreamWaitEvent(hp.s_cc, hp.ev_a, 0);
+  bool equal = colsA % ((size_t)sa.n_gpus * al) == 0;
+  int nrc = 0;
+  if (equal) {
+    nrc = nc.all_gather(dA + c0 * dlda * es, dA, cn * dlda * es, kNcclUint8, sa.comm, hp.s_cc);
+  } else {
+    nrc = nc.group_start();
+    for (int r = 0; !nrc && r < sa.n_gpus; ++r) {
+      size_t r0 = 0, rn = 0;
+      mmbo_shard_columns(colsA, sa.n_gpus, r, al, &r0, &rn);
+      if (rn == 0) continue;
+      char* piece = dA + r0 * dlda * es;
+      nrc = nc.broadcast(piece, piece, rn * dlda * es, kNcclUint8, r, sa.comm, hp.s_cc);
+    }
+    const int end = nc.group_end();
+    if (!nrc) nrc = end;
+  }
+  if (nrc) return MMBO_ERR_NCCL;
+  cudaEventRecord(hp.ev_cc, hp.s_cc);
+  cudaStreamWaitEvent(hp.s_mm, hp.ev_cc, 0);  // the first GEMM needs all of A
+  return MMBO_OK;
+}
+
+static int gemm_host(int dtype, const GemmArgs& h, int kernelId, double alpha64 = 0.0, double beta64 = 0.0,
+                     const ShardedA* sharded_a = nullptr) {
   const size_t es = dtype == MMBO_DTYPE_F64 ? 8 : dtype == MMBO_DTYPE_F32 ? 4 : 2;
   const int dev = current_device();
   if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
@@ -916,12 +1133,17 @@ static int gemm_host(int dtype, const GemmArgs& h, int kernelId, double alpha64 
   char* dC[2] = {dA + a_bytes + 2 * b_bytes, dA + a_bytes + 2 * b_bytes + c_bytes};
   const bool use_c = dtype == MMBO_DTYPE_F64 ? beta64 != 0.0 : h.beta != 0.f;
   cudaError_t e;
-  if (h.k > 0) {
-    e = cudaMemcpy2DAsync(dA, dlda * es, h.A, h.lda * es, rowsA * es, colsA, cudaMemcpyHostToDevice, hp.s_in);
-    if (e != cudaSuccess) return (int)e;
+  if (h.k > 0 && sharded_a && sharded_a->n_gpus > 1) {
+    rc = stage_a_sharded(*sharded_a, hp, h, es, dA, dlda, rowsA, colsA);
+    if (rc) { cudaDeviceSynchronize(); return rc; }
+  } else {
+    if (h.k > 0) {
+      e = cudaMemcpy2DAsync(dA, dlda * es, h.A, h.lda * es, rowsA * es, colsA, cudaMemcpyHostToDevice, hp.s_in);
+      if (e != cudaSuccess) return (int)e;
+    }
+    cudaEventRecord(hp.ev_a, hp.s_in);
+    cudaStreamWaitEvent(hp.s_mm, hp.ev_a, 0);
   }
-  cudaEventRecord(hp.ev_a, hp.s_in);
-  cudaStreamWaitEvent(hp.s_mm, hp.ev_a, 0);
   for (size_t j = 0; j < panels; ++j) {
     const int b = (int)(j & 1);
     const size_t j0 = j * np, w = (j0 + np <= h.n) ? np : h.n - j0;
@@ -953,7 +1175,7 @@ static int gemm_host(int dtype, const GemmArgs& h, int kernelId, double alpha64 
       }
       rc = run_f64(g, alpha64, beta64, id, hp.s_mm);
     } else if (dtype == MMBO_DTYPE_F32) {
-      if (id == MMBO_KERNEL_AUTO) id = select_f32(g);
+      if (id == MMBO_KERNEL_AUTO) id = select_f32_fitting(g);
       rc = run_f32(g, id, hp.s_mm);
     } else {
       if (id == MMBO_KERNEL_AUTO) id = select_f16(g);
@@ -969,6 +1191,7 @@ static int gemm_host(int dtype, const GemmArgs& h, int kernelId, double alpha64 
   // the caller's buffers hold the result when this returns
   if ((e = cudaStreamSynchronize(hp.s_out)) != cudaSuccess) return (int)e;
   if ((e = cudaStreamSynchronize(hp.s_mm)) != cudaSuccess) return (int)e;
+  if ((e = cudaStreamSynchronize(hp.s_cc)) != cudaSuccess) return (int)e;
   return (int)cudaStreamSynchronize(hp.s_in);
 }
 
@@ -989,7 +1212,7 @@ int mmbo_gemm_f32(int transA, int transB, size_t m, size_t n, size_t k, const fl
   g.alpha = *alpha;
   g.beta = *beta;
   if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF32)) return MMBO_ERR_BAD_KERNEL_ID;
-  const int id = kernelId == MMBO_KERNEL_AUTO ? select_f32(g) : kernelId;
+  const int id = kernelId == MMBO_KERNEL_AUTO ? select_f32_fitting(g) : kernelId;
   return run_f32(g, id, static_cast<cudaStream_t>(stream));
 }
 
@@ -1027,6 +1250,99 @@ int mmbo_gemm_f16_bcast(int transA, int transB, size_t m, size_t n, size_t k, co
   g.peers = C_peers;
   g.npeers = npeers;
   return run_f16(g, id, static_cast<cudaStream_t>(stream));
+}
+
+int mmbo_gemm_f16_mcast(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha, const void* A,
+                        size_t lda, const void* B, size_t ldb, const float* beta, void* C, size_t ldc,
+                        void* C_multicast, int kernelId, void* stream) {
+  MMBO_API_LOCK();
+  GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
+  int rc = validate(g, alpha, beta);
+  if (rc) return rc;
+  g.alpha = *alpha;
+  g.beta = *beta;
+  if (!C_multicast) return MMBO_ERR_NULL_POINTER;
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 1 || kernelId >= kNumF16)) return MMBO_ERR_BAD_KERNEL_ID;
+  if (g.m == 0 || g.n == 0) return MMBO_OK;
+  // only the tensor-core kernels' staged epilogue writes whole 16-byte column pieces
+  if (g.k == 0 || !hgemm_tma_ok(g) || !aligned16(g.C) || !aligned16(C_multicast) || g.ldc % 8 != 0 || g.m % 8 != 0)
+    return MMBO_ERR_KERNEL_UNSUITABLE;
+  int id = kernelId == MMBO_KERNEL_AUTO ? select_f16(g) : kernelId;
+  if (id == 0) id = 2;
+  g.c_multicast = C_multicast;
+  return run_f16(g, id, static_cast<cudaStream_t>(stream));
+}
+
+// Checks shared by the multi-GPU entry points; on success (*col0, *ncols) is this rank's block.
+static int shard_check(int nGpus, int rank, void* comm, bool need_comm, size_t n, size_t* col0, size_t* ncols) {
+  if (nGpus <= 0 || nGpus > 64 || rank < 0 || rank >= nGpus) return MMBO_ERR_BAD_SHARD;
+  if (need_comm && nGpus > 1) {
+    if (!comm) return MMBO_ERR_NULL_POINTER;
+    NcclApi& nc = nccl_api();
+    if (!nc.ok()) return MMBO_ERR_NO_NCCL;
+    int cnt = 0, me = -1;
+    if (nc.comm_count(comm, &cnt) || nc.comm_user_rank(comm, &me)) return MMBO_ERR_NCCL;
+    if (cnt != nGpus || me != rank) return MMBO_ERR_BAD_SHARD;  // the communicator is not the one described
+  }
+  return mmbo_shard_columns(n, nGpus, rank, 256, col0, ncols);
+}
+
+int mmbo_gemm_f16_sharded(int nGpus, int rank, void* ncclComm, int gatherC, int transA, int transB, size_t m,
+                          size_t n, size_t k, const float* alpha, const void* A, size_t lda, const void* B_block,
+                          size_t ldb, const float* beta, void* C, size_t ldc, int kernelId, void* stream) {
+  MMBO_API_LOCK();
+  size_t col0 = 0, ncols = 0;
+  int rc = shard_check(nGpus, rank, ncclComm, gatherC != 0, n, &col0, &ncols);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* c_block = C ? static_cast<char*>(C) + col0 * ldc * 2 : nullptr;
+  GemmArgs g{transA, transB, m, ncols, k, A, B_block, c_block, lda, ldb, ldc, 0.f, 0.f};
+  if ((rc = validate(g, alpha, beta))) return rc;
+  g.alpha = *alpha;
+  g.beta = *beta;
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF16)) return MMBO_ERR_BAD_KERNEL_ID;
+  if (gatherC && nGpus > 1 && ldc != m) return MMBO_ERR_BAD_SHARD;  // column blocks must be contiguous to be exchanged
+  if (m == 0 || n == 0) return MMBO_OK;
+  if (ncols > 0) {
+    const int id = kernelId == MMBO_KERNEL_AUTO ? select_f16(g) : kernelId;
+    if ((rc = run_f16(g, id, st))) return rc;
+  }
+  if (!gatherC || nGpus == 1) return MMBO_OK;
+  NcclApi& nc = nccl_api();
+  int nrc = 0;
+  if (n % ((size_t)nGpus * 256) == 0) {  // equal blocks: one all-gather in place
+    nrc = nc.all_gather(c_block, C, m * ncols, kNcclFloat16, ncclComm, st);
+  } else {
+    nrc = nc.group_start();
+    for (int r = 0; !nrc && r < nGpus; ++r) {
+      size_t r0 = 0, rn = 0;
+      mmbo_shard_columns(n, nGpus, r, 256, &r0, &rn);
+      if (rn == 0) continue;
+      char* piece = static_cast<char*>(C) + r0 * ldc * 2;
+      nrc = nc.broadcast(piece, piece, m * rn, kNcclFloat16, r, ncclComm, st);
+    }
+    const int end = nc.group_end();
+    if (!nrc) nrc = end;
+  }
+  return nrc ? MMBO_ERR_NCCL : MMBO_OK;
+}
+
+int mmbo_gemm_f16_sharded_host(int nGpus, int rank, void* ncclComm, int transA, int transB, size_t m, size_t n,
+                               size_t k, const float* alpha, const void* A, size_t lda, const void* B_block,
+                               size_t ldb, const float* beta, void* C_block, size_t ldc, int kernelId) {
+  MMBO_API_LOCK();
+  size_t col0 = 0, ncols = 0;
+  int rc = shard_check(nGpus, rank, ncclComm, true, n, &col0, &ncols);
+  if (rc) return rc;
+  GemmArgs g{transA, transB, m, ncols, k, A, B_block, C_block, lda, ldb, ldc, 0.f, 0.f};
+  if (ncols == 0) g.C = g.C ? g.C : const_cast<void*>(A);  // an empty block still takes part in the exchange of A
+  if ((rc = validate(g, alpha, beta))) return rc;
+  g.alpha = *alpha;
+  g.beta = *beta;
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= kNumF16)) return MMBO_ERR_BAD_KERNEL_ID;
+  if (m == 0 || n == 0) return MMBO_OK;
+  const ShardedA sa{nGpus, rank, ncclComm};
+  return gemm_host(MMBO_DTYPE_F16, g, kernelId, 0.0, 0.0, &sa);
 }
 
 int mmbo_gemm_f32_host(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha, const float* A,
@@ -1082,30 +1398,102 @@ int mmbo_gemm_f64_host(int transA, int transB, size_t m, size_t n, size_t k, con
   return gemm_host(MMBO_DTYPE_F64, g, kernelId, *alpha, *beta);
 }
 
+// One launch for the whole batch where the chosen kernel can address it (the problem index is a
+// coordinate of its tile walk or the third grid dimension); otherwise one call per problem.
+static bool batch_in_one_launch(int dtype, int id, const GemmArgs& g) {
+  if (g.batch <= 1) return true;
+  if (g.batch > 65535) return false;
+  if (g.k == 0 || id == 0) return true;  // grid z, any strides
+  if (dtype == MMBO_DTYPE_F16)  // tensor maps over the caller's operands: strides in whole 16-byte units
+    return hgemm_tma_ok(g) && batch_stride_ok(g.batch, g.sA, 2) && batch_stride_ok(g.batch, g.sB, 2);
+  if (dtype == MMBO_DTYPE_F32) return id != 6;  // ids 1, 2: grid z; 3-5: the split pass reads any strides
+  return true;                                  // fp64: grid z, or pointer offsets where TMA cannot take the stride
+}
+
 int mmbo_gemm_strided_batched(int dtype, int transA, int transB, size_t m, size_t n, size_t k, const void* alpha,
                               const void* A, size_t lda, size_t strideA, const void* B, size_t ldb, size_t strideB,
                               const void* beta, void* C, size_t ldc, size_t strideC, size_t batch, int kernelId,
                               void* stream) {
+  MMBO_API_LOCK();
   if (dtype != MMBO_DTYPE_F16 && dtype != MMBO_DTYPE_F32 && dtype != MMBO_DTYPE_F64) return MMBO_ERR_BAD_DTYPE;
+  GemmArgs g{transA, transB, m, n, k, A, B, C, lda, ldb, ldc, 0.f, 0.f};
+  int rc = validate(g, static_cast<const float*>(alpha), static_cast<const float*>(beta));
+  if (rc) return rc;
+  int count = 0;
+  rows_of(dtype, &count);
+  if (kernelId != MMBO_KERNEL_AUTO && (kernelId < 0 || kernelId >= count)) return MMBO_ERR_BAD_KERNEL_ID;
+  if (batch == 0 || m == 0 || n == 0) return MMBO_OK;
+  double alpha64 = 0.0, beta64 = 0.0;
+  if (dtype == MMBO_DTYPE_F64) {
+    alpha64 = *static_cast<const double*>(alpha);
+    beta64 = *static_cast<const double*>(beta);
+  } else {
+    g.alpha = *static_cast<const float*>(alpha);
+    g.beta = *static_cast<const float*>(beta);
+  }
+  g.batch = batch; g.sA = strideA; g.sB = strideB; g.sC = strideC;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int id = kernelId;
+  if (id == MMBO_KERNEL_AUTO) {
+    if (dtype == MMBO_DTYPE_F16) id = select_f16(g);
+    else if (dtype == MMBO_DTYPE_F32) id = select_f32_fitting(g);
+    else {
+      id = g.k == 0 ? 0 : tune_lookup(MMBO_DTYPE_F64, g);
+      if (id < 0) id = select_f64(g);
+    }
+  }
+  if (batch_in_one_launch(dtype, id, g)) {
+    if (dtype == MMBO_DTYPE_F16) rc = run_f16(g, id, st);
+    else if (dtype == MMBO_DTYPE_F32) rc = run_f32(g, id, st);
+    else rc = run_f64(g, alpha64, beta64, id, st);
+    // a stride the tensor maps refuse (the driver has the last word): one call per problem instead
+    if (rc != MMBO_ERR_TENSOR_MAP) return rc;
+  }
   const size_t es = dtype == MMBO_DTYPE_F16 ? 2 : dtype == MMBO_DTYPE_F32 ? 4 : 8;
+  GemmArgs one = g;
+  one.batch = 1; one.sA = one.sB = one.sC = 0;
   for (size_t b = 0; b < batch; ++b) {
-    const char* a = static_cast<const char*>(A) + (A ? b * strideA * es : 0);
-    const char* bb = static_cast<const char*>(B) + (B ? b * strideB * es : 0);
-    char* c = static_cast<char*>(C) + (C ? b * strideC * es : 0);
-    int rc;
-    if (dtype == MMBO_DTYPE_F16)
-      rc = mmbo_gemm_f16(transA, transB, m, n, k, static_cast<const float*>(alpha), a, lda, bb, ldb,
-                         static_cast<const float*>(beta), c, ldc, kernelId, stream);
-    else if (dtype == MMBO_DTYPE_F32)
-      rc = mmbo_gemm_f32(transA, transB, m, n, k, static_cast<const float*>(alpha), reinterpret_cast<const float*>(a),
-                         lda, reinterpret_cast<const float*>(bb), ldb, static_cast<const float*>(beta),
-                         reinterpret_cast<float*>(c), ldc, kernelId, stream);
-    else
-      rc = mmbo_gemm_f64(transA, transB, m, n, k, static_cast<const double*>(alpha), reinterpret_cast<const double*>(a),
-                         lda, reinterpret_cast<const double*>(bb), ldb, static_cast<const double*>(beta),
-                         reinterpret_cast<double*>(c), ldc, kernelId, stream);
+    one.A = static_cast<const char*>(A) + (A ? b * strideA * es : 0);
+    one.B = static_cast<const char*>(B) + (B ? b * strideB * es : 0);
+    one.C = static_cast<char*>(C) + b * strideC * es;
+    if (dtype == MMBO_DTYPE_F16) rc = run_f16(one, id, st);
+    else if (dtype == MMBO_DTYPE_F32) rc = run_f32(one, id, st);
+    else rc = run_f64(one, alpha64, beta64, id, st);
     if (rc) return rc;
   }
+  return MMBO_OK;
+}
+
+unsigned long long mmbo_launch_count(void) {
+  MMBO_API_LOCK();
+  return g_launch_count;
+}
+
+int mmbo_set_option(const char* name, unsigned int value) {
+  MMBO_API_LOCK();
+  if (!name) return MMBO_ERR_NULL_POINTER;
+  Settings& s = settings();
+  if (!strcmp(name, "diag")) s.diag = value;
+  else if (!strcmp(name, "wgm")) s.wgm = value;
+  else if (!strcmp(name, "tf32_chunk")) s.tf32_chunk = value ? value : 1;
+  else if (!strcmp(name, "f32_exact")) s.f32_exact = value;
+  else if (!strcmp(name, "dgemm_stage_c")) s.dgemm_stage_c = value;
+  else if (!strcmp(name, "split_k")) s.split_k = value;
+  else return MMBO_ERR_BAD_OPTION;
+  return MMBO_OK;
+}
+
+int mmbo_get_option(const char* name, unsigned int* value) {
+  MMBO_API_LOCK();
+  if (!name || !value) return MMBO_ERR_NULL_POINTER;
+  const Settings& s = settings();
+  if (!strcmp(name, "diag")) *value = s.diag;
+  else if (!strcmp(name, "wgm")) *value = s.wgm;
+  else if (!strcmp(name, "tf32_chunk")) *value = s.tf32_chunk;
+  else if (!strcmp(name, "f32_exact")) *value = s.f32_exact;
+  else if (!strcmp(name, "dgemm_stage_c")) *value = s.dgemm_stage_c;
+  else if (!strcmp(name, "split_k")) *value = s.split_k;
+  else return MMBO_ERR_BAD_OPTION;
   return MMBO_OK;
 }
 
@@ -1170,6 +1558,9 @@ const char* mmbo_status_string(int status) {
     case MMBO_ERR_TOO_LARGE: return "problem exceeds launch limits of the chosen kernel";
     case MMBO_ERR_WORKSPACE: return "the workspace lent by the caller is too small for this call";
     case MMBO_ERR_TUNING_FILE: return "tuning file missing or malformed";
+    case MMBO_ERR_BAD_OPTION: return "unknown option name";
+    case MMBO_ERR_NCCL: return "an NCCL call on the caller's communicator failed";
+    case MMBO_ERR_NO_NCCL: return "libnccl.so.2 could not be found in the process";
     case MMBO_ERR_NOALLOC_TOO_LARGE:
       return "problem needs more scratch than the library's built-in MMBO_NOALLOC_SCRATCH_BYTES";
   }
@@ -1255,12 +1646,15 @@ int mmbo_set_workspace(void* ptr, size_t bytes) {
   MMBO_API_LOCK();
   const int dev = current_device();
   if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
+  // reject before touching any state: a refused call leaves the library as it was
+  if (ptr && (reinterpret_cast<uintptr_t>(ptr) & 1023u)) return MMBO_ERR_WORKSPACE;
   Workspace& w = g_ws[dev];
   if (!w.user && w.ptr) {
-    cudaError_t e = cudaFree(w.ptr);
+    cudaError_t e = cudaFree(w.ptr);  // waits for the kernels still using it
+    w.ptr = nullptr;
+    w.bytes = 0;
     if (e != cudaSuccess) return (int)e;
   }
-  if (ptr && (reinterpret_cast<uintptr_t>(ptr) & 1023u)) return MMBO_ERR_WORKSPACE;
   w.ptr = ptr;
   w.bytes = ptr ? bytes : 0;
   w.user = ptr != nullptr;
@@ -1357,7 +1751,7 @@ int mmbo_gemm_f32_noalloc(int transA, int transB, size_t m, size_t n, size_t k, 
     if (e != cudaSuccess) return (int)e;
     g_noalloc_scratch_addr[dev] = ptr;
   }
-  return run_tf32x3<128, 3, 1>(g, g_noalloc_scratch_addr[dev], env_u32("MMBO_WGM", kF32Rows[4].wgm), st);
+  return run_tf32x3<128, 3, 1>(g, g_noalloc_scratch_addr[dev], wgm_of(kF32Rows[4]), st);
 }
 
 }  // extern "C"

@@ -196,6 +196,36 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       : "memory");
 }
 
+// 3-D forms: the third coordinate is the problem index of a strided batch (the tensor map's
+// outermost dimension, one problem per index); it has no alignment rule.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int32_t c0, int32_t c1, int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map,
+                                                 uint32_t cluster_bar, int32_t c0, int32_t c1, int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int32_t c0, int32_t c1, int32_t c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1),
+               "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int32_t c0, int32_t c1,
+                                             int32_t c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+
 // Asks L2 to fetch a tile ahead of the load that will need it (no shared memory involved).
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int32_t c0, int32_t c1) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1)
@@ -206,6 +236,38 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
                                              int32_t c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+
+// Single problems keep 2-D tensor maps and the 2-D instruction forms; a strided batch uses 3-D maps.
+// `batched` is uniform over the grid, so the branch costs nothing.
+__device__ __forceinline__ void tma_load_tile(bool batched, uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                              int32_t c0, int32_t c1, int32_t c2) {
+  if (batched) tma_load_3d(dst, map, bar, c0, c1, c2);
+  else tma_load_2d(dst, map, bar, c0, c1);
+}
+__device__ __forceinline__ void tma_load_tile_pair(bool batched, uint32_t dst, const CUtensorMap* map,
+                                                   uint32_t cluster_bar, int32_t c0, int32_t c1, int32_t c2) {
+  if (batched) tma_load_3d_pair(dst, map, cluster_bar, c0, c1, c2);
+  else tma_load_2d_pair(dst, map, cluster_bar, c0, c1);
+}
+__device__ __forceinline__ void tma_prefetch_l2_tile(bool batched, const CUtensorMap* map, int32_t c0, int32_t c1,
+                                                     int32_t c2) {
+  if (batched) tma_prefetch_l2_3d(map, c0, c1, c2);
+  else tma_prefetch_l2_2d(map, c0, c1);
+}
+__device__ __forceinline__ void tma_store_tile(bool batched, const CUtensorMap* map, uint32_t src, int32_t c0,
+                                               int32_t c1, int32_t c2) {
+  if (batched) tma_store_3d(map, src, c0, c1, c2);
+  else tma_store_2d(map, src, c0, c1);
+}
+
+// 16-byte store to a multicast address (an address range that NVSwitch maps onto the same offset
+// of a buffer in several GPUs): every GPU bound to the range receives the data.  A store only;
+// nothing is ever loaded through such an address here.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
                : "memory");
 }
 

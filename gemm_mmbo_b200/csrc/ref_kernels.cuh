@@ -33,7 +33,11 @@ __device__ __forceinline__ double from_f32<double>(float v) { return (double)v; 
 template <typename T>
 __global__ void gemm_simple_kernel(int transA, int transB, size_t m, size_t n, size_t k, float alpha,
                                    const T* __restrict__ A, size_t lda, const T* __restrict__ B,
-                                   size_t ldb, float beta, T* __restrict__ C, size_t ldc) {
+                                   size_t ldb, float beta, T* __restrict__ C, size_t ldc, size_t batch_a,
+                                   size_t batch_b, size_t batch_c) {
+  A += (size_t)blockIdx.z * batch_a;  // problem blockIdx.z of a strided batch
+  B += (size_t)blockIdx.z * batch_b;
+  C += (size_t)blockIdx.z * batch_c;
   const size_t i = (size_t)blockIdx.x * 32 + threadIdx.x;
   const size_t j = (size_t)blockIdx.y * 8 + threadIdx.y;
   if (i >= m || j >= n) return;
@@ -51,7 +55,11 @@ __global__ void gemm_simple_kernel(int transA, int transB, size_t m, size_t n, s
 // binary64 variant of the kernel above (accumulation and scalars in binary64).
 __global__ void gemm_simple_f64_kernel(int transA, int transB, size_t m, size_t n, size_t k, double alpha,
                                        const double* __restrict__ A, size_t lda, const double* __restrict__ B,
-                                       size_t ldb, double beta, double* __restrict__ C, size_t ldc) {
+                                       size_t ldb, double beta, double* __restrict__ C, size_t ldc, size_t batch_a,
+                                       size_t batch_b, size_t batch_c) {
+  A += (size_t)blockIdx.z * batch_a;
+  B += (size_t)blockIdx.z * batch_b;
+  C += (size_t)blockIdx.z * batch_c;
   const size_t i = (size_t)blockIdx.x * 32 + threadIdx.x;
   const size_t j = (size_t)blockIdx.y * 8 + threadIdx.y;
   if (i >= m || j >= n) return;
@@ -66,7 +74,9 @@ __global__ void gemm_simple_f64_kernel(int transA, int transB, size_t m, size_t 
   C[i + j * ldc] = r;
 }
 
-__global__ void scale_c_f64_kernel(size_t m, size_t n, double beta, double* __restrict__ C, size_t ldc) {
+__global__ void scale_c_f64_kernel(size_t m, size_t n, double beta, double* __restrict__ C, size_t ldc,
+                                   size_t batch_c) {
+  C += (size_t)blockIdx.z * batch_c;
   const size_t i = (size_t)blockIdx.x * 32 + threadIdx.x;
   const size_t j = (size_t)blockIdx.y * 8 + threadIdx.y;
   if (i >= m || j >= n) return;
@@ -75,7 +85,8 @@ __global__ void scale_c_f64_kernel(size_t m, size_t n, double beta, double* __re
 
 // k == 0: C = beta*C (or zero when beta == 0).
 template <typename T>
-__global__ void scale_c_kernel(size_t m, size_t n, float beta, T* __restrict__ C, size_t ldc) {
+__global__ void scale_c_kernel(size_t m, size_t n, float beta, T* __restrict__ C, size_t ldc, size_t batch_c) {
+  C += (size_t)blockIdx.z * batch_c;
   const size_t i = (size_t)blockIdx.x * 32 + threadIdx.x;
   const size_t j = (size_t)blockIdx.y * 8 + threadIdx.y;
   if (i >= m || j >= n) return;

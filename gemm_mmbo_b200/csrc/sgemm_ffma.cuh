@@ -27,6 +27,9 @@ struct SgemmParams {
   float alpha, beta;
   uint32_t wgm;
   uint32_t vec_a, vec_b, vec_c;  // 1 when 128-bit accesses to that operand are legal
+  // strided batch (the reference's kernel takes the problem index from the third grid dimension,
+  // src/gemm/ref/Kernels.cpp:254): elements between consecutive problems' A, B, C
+  unsigned long long batch_a, batch_b, batch_c;
 };
 
 // Loads a (ROWS x BK) slab of an operand into registers.  "row" is the M (or N) index
@@ -129,6 +132,9 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
 
   const int tid = threadIdx.x;
   const int tx = tid % TX, ty = tid / TX;
+  A += (size_t)blockIdx.z * p.batch_a;  // problem blockIdx.z of a strided batch
+  B += (size_t)blockIdx.z * p.batch_b;
+  C += (size_t)blockIdx.z * p.batch_c;
 
   uint32_t tile_m, tile_n;
   mmbo_wgm_remap(blockIdx.x, blockIdx.y, gridDim.x, gridDim.y, p.wgm, &tile_m, &tile_n);

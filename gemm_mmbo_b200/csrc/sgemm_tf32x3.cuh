@@ -54,9 +54,13 @@ constexpr int kSplitTile = 64;
 template <bool ROW_CONTIG>
 __global__ void __launch_bounds__(256)
 split_pack_kernel(const float* __restrict__ X, size_t ld, uint32_t R, uint32_t K, uint32_t Kpad,
-                  float* __restrict__ hi, float* __restrict__ lo) {
+                  float* __restrict__ hi, float* __restrict__ lo, size_t x_batch_stride) {
   __shared__ float tile[kSplitTile][kSplitTile + 1];  // [l][r], used by the transposing variant
   const uint32_t tid = threadIdx.x;
+  // strided batch: problem blockIdx.z; its packed rows follow the previous problem's
+  X += (size_t)blockIdx.z * x_batch_stride;
+  hi += (size_t)blockIdx.z * R * Kpad;
+  lo += (size_t)blockIdx.z * R * Kpad;
   const uint32_t l0 = blockIdx.x * kSplitTile, r0 = blockIdx.y * kSplitTile;
   if (ROW_CONTIG) {
 #pragma unroll
@@ -117,6 +121,8 @@ struct TfSmem {
 struct TfParams {
   uint32_t m, n, k;
   uint32_t tiles_m, tiles_n;
+  uint32_t batch;                     // problems of a strided batch; the walk covers batch * tiles_m * tiles_n tiles
+  unsigned long long c_batch_stride;  // elements between the C of consecutive problems (plain epilogue)
   uint32_t wgm;
   float alpha, beta;
   float* c;        // used by the plain epilogue
@@ -150,8 +156,15 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
   uint32_t cta_rank = 0;
   if constexpr (CG == 2) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta_rank));
   const uint32_t walker = blockIdx.x / CG, num_walkers = gridDim.x / CG;
-  const uint32_t num_tiles = p.tiles_m * p.tiles_n;
+  const uint32_t tiles_per_problem = p.tiles_m * p.tiles_n;
+  const uint32_t num_tiles = tiles_per_problem * p.batch;
   const uint32_t num_kb = (p.k + kTfBlockK - 1) / kTfBlockK;
+  const bool batched = p.batch > 1u;  // 3-D tensor maps; single problems keep the 2-D forms
+  auto locate = [&](uint32_t tile, uint32_t* tm, uint32_t* tn) -> uint32_t {
+    const uint32_t prob = tile / tiles_per_problem;
+    mmbo_tile_from_serial(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, p.wgm, tm, tn);
+    return prob;
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0u;
@@ -198,7 +211,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
       bool ok = true;
       for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers) {
         uint32_t tm_idx, tn_idx;
-        mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
+        const int32_t prob = static_cast<int32_t>(locate(tile, &tm_idx, &tn_idx));
         const int32_t m0 = static_cast<int32_t>(tm_idx * TM + cta_rank * L::kAopRows);
         const int32_t n0 = static_cast<int32_t>((tn_idx * CG + cta_rank) * kTfTileN);
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
@@ -211,8 +224,8 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
           const int32_t k0 = static_cast<int32_t>(kb * kTfBlockK);
           if (cta_rank == 0) mbar_expect_tx(full_bar(stage), L::kStageBytes * CG);
           auto load = [&](uint32_t dst, const CUtensorMap* map, int32_t c1) {
-            if constexpr (CG == 2) tma_load_2d_pair(dst, map, bar, k0, c1);
-            else tma_load_2d(dst, map, bar, k0, c1);
+            if constexpr (CG == 2) tma_load_tile_pair(batched, dst, map, bar, k0, c1, prob);
+            else tma_load_tile(batched, dst, map, bar, k0, c1, prob);
           };
           load(s0, &tmap_b_hi, n0);                                       // box {32 k, 128 n}
           load(s0 + L::kBopBytes, &tmap_b_lo, n0);
@@ -315,7 +328,8 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
     bool ok = true;
     for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers) {
       uint32_t tm_idx, tn_idx;
-      mmbo_tile_from_serial(tile, p.tiles_m, p.tiles_n, p.wgm, &tm_idx, &tn_idx);
+      const int32_t prob = static_cast<int32_t>(locate(tile, &tm_idx, &tn_idx));
+      float* const c_plain = p.c + static_cast<size_t>(prob) * p.c_batch_stride;
       const uint32_t m0 = tm_idx * TM + col_base;
       const uint32_t ncol0 = (tn_idx * CG + cta_rank) * kTfTileN + 32u * q;
       // running sums of this thread's C column over the tile's TM rows
@@ -369,8 +383,8 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
           __syncwarp();
           if (load_c && lane == 0) {
             mbar_expect_tx(cload_bar(epi_w, b), kTfEpiBufBytes);
-            tma_load_2d(sbuf, &tmap_c, cload_bar(epi_w, b), static_cast<int32_t>(mrow0),
-                        static_cast<int32_t>(ncol0));
+            tma_load_tile(batched, sbuf, &tmap_c, cload_bar(epi_w, b), static_cast<int32_t>(mrow0),
+                        static_cast<int32_t>(ncol0), prob);
           }
           if (load_c) {
             if (!mbar_wait(cload_bar(epi_w, b), cphase[b], abort_flag, kFaultWaitCLoad, epi_w)) ok = false;
@@ -385,7 +399,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
             for (uint32_t t = 0; t < 32; ++t) {
               const uint32_t nj = ncol0 + t;
               float v = 0.f;
-              if (mi < p.m && nj < p.n) v = p.c[(size_t)mi + (size_t)nj * p.ldc];
+              if (mi < p.m && nj < p.n) v = c_plain[(size_t)mi + (size_t)nj * p.ldc];
               gbuf[t * 32u + ((((lane >> 2) ^ (t & 7u)) << 2) | (lane & 3u))] = v;
             }
             __syncwarp();
@@ -410,7 +424,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
           __syncwarp();
           if (lane == 0) {
             if (in_range && ok)
-              tma_store_2d(&tmap_c, sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0));
+              tma_store_tile(batched, &tmap_c, sbuf, static_cast<int32_t>(mrow0), static_cast<int32_t>(ncol0), prob);
             tma_store_commit();
           }
         } else {
@@ -421,7 +435,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
             for (uint32_t t = 0; t < 32; ++t) {
               const uint32_t nj = ncol0 + t;
               const float v = gbuf[t * 32u + ((((lane >> 2) ^ (t & 7u)) << 2) | (lane & 3u))];
-              if (mi < p.m && nj < p.n) p.c[(size_t)mi + (size_t)nj * p.ldc] = v;
+              if (mi < p.m && nj < p.n) c_plain[(size_t)mi + (size_t)nj * p.ldc] = v;
             }
           }
         }

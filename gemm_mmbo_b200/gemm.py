@@ -82,6 +82,45 @@ def gemm_bcast(transA: bool, transB: bool, m: int, n: int, k: int, alpha: float,
         raise MmboError(rc, "mmbo_gemm_f16_bcast")
 
 
+def gemm_mcast(transA: bool, transB: bool, m: int, n: int, k: int, alpha: float, A, lda: int, B, ldb: int,
+               beta: float, C, ldc: int, C_multicast, kernelId: int = KERNEL_AUTO, stream=None) -> None:
+    """fp16 GEMM whose epilogue writes the result once to `C_multicast`, a multicast address of the C
+    window (NVSwitch delivers every store to all GPUs bound to it); old C is read from `C`."""
+    a, b = ctypes.c_float(alpha), ctypes.c_float(beta)
+    rc = LIB.mmbo_gemm_f16_mcast(int(bool(transA)), int(bool(transB)), m, n, k, ctypes.byref(a), _addr(A), lda,
+                                 _addr(B), ldb, ctypes.byref(b), _addr(C), ldc, _addr(C_multicast), kernelId,
+                                 _stream(stream))
+    if rc != 0:
+        raise MmboError(rc, "mmbo_gemm_f16_mcast")
+
+
+def gemm_sharded(n_gpus: int, rank: int, nccl_comm: int | None, gather_c: bool, transA: bool, transB: bool, m: int,
+                 n: int, k: int, alpha: float, A, lda: int, B_block, ldb: int, beta: float, C, ldc: int,
+                 kernelId: int = KERNEL_AUTO, stream=None) -> None:
+    """This rank's part of an fp16 GEMM sharded by column blocks (mmbo_gemm_f16_sharded): C is the whole
+    m x n matrix on this GPU, B_block this rank's block of op(B); with gather_c the blocks are exchanged
+    over NCCL (`nccl_comm`: address of the ncclComm_t) so that every rank ends with all of C."""
+    a, b = ctypes.c_float(alpha), ctypes.c_float(beta)
+    rc = LIB.mmbo_gemm_f16_sharded(n_gpus, rank, nccl_comm, int(bool(gather_c)), int(bool(transA)), int(bool(transB)),
+                                   m, n, k, ctypes.byref(a), _addr(A), lda, _addr(B_block), ldb, ctypes.byref(b),
+                                   _addr(C), ldc, kernelId, _stream(stream))
+    if rc != 0:
+        raise MmboError(rc, "mmbo_gemm_f16_sharded")
+
+
+def gemm_sharded_host(n_gpus: int, rank: int, nccl_comm: int | None, transA: bool, transB: bool, m: int, n: int,
+                      k: int, alpha: float, A, lda: int, B_block, ldb: int, beta: float, C_block, ldc: int,
+                      kernelId: int = KERNEL_AUTO) -> None:
+    """The same on host operands (mmbo_gemm_f16_sharded_host): each rank uploads its share of A, the shares
+    are exchanged between the GPUs over NVLink; B_block / C_block are this rank's column blocks."""
+    a, b = ctypes.c_float(alpha), ctypes.c_float(beta)
+    rc = LIB.mmbo_gemm_f16_sharded_host(n_gpus, rank, nccl_comm, int(bool(transA)), int(bool(transB)), m, n, k,
+                                        ctypes.byref(a), _haddr(A), lda, _haddr(B_block), ldb, ctypes.byref(b),
+                                        _haddr(C_block), ldc, kernelId)
+    if rc != 0:
+        raise MmboError(rc, "mmbo_gemm_f16_sharded_host")
+
+
 def gemm_host(dtype, transA: bool, transB: bool, m: int, n: int, k: int, alpha: float, A, lda: int, B,
               ldb: int, beta: float, C, ldc: int, kernelId: int = KERNEL_AUTO) -> None:
     """Same GEMM with A, B, C in host memory (pinned torch tensors, numpy arrays or raw
@@ -236,3 +275,23 @@ def tuning_load(path) -> None:
 
 def tuning_clear() -> None:
     LIB.mmbo_tuning_clear()
+
+
+def set_option(name: str, value: int) -> None:
+    """Set one of the library's experiment / diagnosis switches (see mmbo_set_option)."""
+    rc = LIB.mmbo_set_option(name.encode(), int(value))
+    if rc != 0:
+        raise MmboError(rc, "mmbo_set_option")
+
+
+def get_option(name: str) -> int:
+    v = ctypes.c_uint32()
+    rc = LIB.mmbo_get_option(name.encode(), ctypes.byref(v))
+    if rc != 0:
+        raise MmboError(rc, "mmbo_get_option")
+    return v.value
+
+
+def launch_count() -> int:
+    """Kernel launches the library has queued since it was loaded."""
+    return int(LIB.mmbo_launch_count())

@@ -113,8 +113,8 @@ int main(int argc, char** argv) {
   // one call of the library for the chosen dtype (binary64 takes double scalars, like the reference)
   auto gemm_call = [&](int id) -> int {
     if (o.dtype == MMBO_DTYPE_F64)
-      return ::dgemm(o.transA, o.transB, o.M, o.N, o.K, &alpha64, (const double*)dA, o.lda, (const double*)dB,
-                         o.ldb, &beta64, (double*)dC, o.ldc, id);
+      return mmbo::launchGemm(o.dtype, o.transA, o.transB, o.M, o.N, o.K, &alpha64, dA, o.lda, dB, o.ldb, &beta64, dC,
+                              o.ldc, id);
     return mmbo::launchGemm(o.dtype, o.transA, o.transB, o.M, o.N, o.K, &o.alpha, dA, o.lda, dB, o.ldb, &o.beta, dC,
                             o.ldc, id);
   };

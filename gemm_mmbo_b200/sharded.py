@@ -123,6 +123,50 @@ class ColumnShard:
             C_sym.barrier()
 
 
+    def gemm_and_multicast(self, transA, transB, m, k, alpha, A, lda, B_block, ldb, beta, C_sym: "SymmetricC",
+                           kernelId=_g.KERNEL_AUTO, stream=None, barrier: bool = True):
+        """The same exchange through the multicast address of the symmetric allocation: the epilogue writes
+        every finished piece once (multimem.st) and NVSwitch delivers it to every rank's copy of C, this
+        rank's included.  Needs `C_sym.multicast_ptr` (NVLink multicast support)."""
+        if not C_sym.multicast_ptr:
+            raise RuntimeError("this symmetric allocation has no multicast mapping")
+        off = self.col0 * m * 2
+        _g.gemm_mcast(transA, transB, m, self.ncols, k, alpha, A, lda, B_block, ldb, beta, C_sym.ptrs[self.rank] + off,
+                      m, C_sym.multicast_ptr + off, kernelId, stream)
+        if barrier:
+            C_sym.barrier()
+
+    # ---- the C-ABI multi-GPU entry points ---------------------------------------------------
+    def gemm_sharded(self, transA, transB, m, k, alpha, A, lda, B_block, ldb, beta, C_full, gather_c: bool = True,
+                     comm: int | None = None, kernelId=_g.KERNEL_AUTO, stream=None):
+        """mmbo_gemm_f16_sharded: this rank's block of C_full (the whole m x n C on this GPU) is computed in
+        place and, with gather_c, the blocks are exchanged through the caller's NCCL communicator."""
+        if comm is None and gather_c and self.world > 1:
+            comm = nccl_comm_ptr()
+        _g.gemm_sharded(self.world, self.rank, comm, gather_c, transA, transB, m, self.n, k, alpha, A, lda, B_block,
+                        ldb, beta, C_full, m, kernelId, stream)
+
+    def gemm_sharded_host(self, transA, transB, m, k, alpha, hA, lda, hB_block, ldb, beta, hC_block, ldc,
+                          comm: int | None = None, kernelId=_g.KERNEL_AUTO):
+        """mmbo_gemm_f16_sharded_host: host operands; each rank uploads 1 / world of A and the GPUs exchange
+        the shares over NVLink."""
+        if comm is None and self.world > 1:
+            comm = nccl_comm_ptr()
+        _g.gemm_sharded_host(self.world, self.rank, comm, transA, transB, m, self.n, k, alpha, hA, lda, hB_block, ldb,
+                             beta, hC_block, ldc, kernelId)
+
+
+def nccl_comm_ptr(group=None) -> int:
+    """Address of the ncclComm_t behind a torch.distributed NCCL process group (what the C ABI's multi-GPU
+    entry points take).  The communicator is created by the group's first collective; one is issued here."""
+    import torch
+    import torch.distributed as dist
+    group = dist.group.WORLD if group is None else group
+    dist.all_reduce(torch.zeros(1, device="cuda"), group=group)
+    torch.cuda.synchronize()
+    return int(group._get_backend(torch.device("cuda"))._comm_ptr())
+
+
 class SymmetricC:
     """The full column-major C (n columns of m fp16 elements) allocated in symmetric memory:
     `tensor` is this rank's copy, `ptrs[r]` the address at which rank r's copy is mapped into
@@ -137,6 +181,8 @@ class SymmetricC:
         self._hdl = symm_mem.rendezvous(self.tensor, group)
         self.ptrs = [int(p) for p in self._hdl.buffer_ptrs]
         self.rank, self.world = self._hdl.rank, self._hdl.world_size
+        # address of the same buffer in the NVLink multicast mapping (0: no multicast support here)
+        self.multicast_ptr = int(getattr(self._hdl, "multicast_ptr", 0) or 0)
 
     def barrier(self):
         """All ranks' work queued so far on their current streams has finished (stream-ordered)."""

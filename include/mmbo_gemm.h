@@ -56,6 +56,9 @@ extern "C" {
 #define MMBO_ERR_WORKSPACE (-15)        /* lent workspace too small or misaligned */
 #define MMBO_ERR_TUNING_FILE (-17)      /* tuning file missing or malformed */
 #define MMBO_ERR_NOALLOC_TOO_LARGE (-16) /* mmbo_gemm_f32_noalloc: scratch need exceeds the built-in array */
+#define MMBO_ERR_BAD_OPTION (-18)       /* mmbo_set_option / mmbo_get_option: unknown name */
+#define MMBO_ERR_NCCL (-19)             /* an NCCL call on the caller's communicator failed */
+#define MMBO_ERR_NO_NCCL (-20)          /* no libnccl.so.2 in the process or on the loader path */
 
 /* SGEMM, fp32 storage and arithmetic.  Replaces dgemm_NT / naive_dgemm
  * (src/gemm/gemm.h:47-48, :4-5) for dtype fp32; kernelId indexes the fp32 kernel table
@@ -85,6 +88,51 @@ int mmbo_gemm_f16_bcast(int transA, int transB, size_t m, size_t n, size_t k, co
                         const void* A, size_t lda, const void* B, size_t ldb, const float* beta,
                         void* C, size_t ldc, void* const* C_peers, int npeers, int kernelId,
                         void* stream);
+
+/* The same exchange through one multicast address.  C_multicast is the address of C(0,0) in a
+ * multicast mapping of the buffers that hold C on the GPUs of the node (NVLink multicast object:
+ * cuMulticastCreate / cuMulticastBindMem, or the multicast pointer of a symmetric-memory
+ * allocation); C is this GPU's own, ordinary address of the same window.  The epilogue writes
+ * every finished piece once, with multimem.st, to C_multicast -- the switch delivers it to every
+ * bound GPU, this one included -- so the result leaves this GPU once instead of once per peer.
+ * With beta != 0 the old values are read from C.  Same requirements as mmbo_gemm_f16_bcast.
+ * The process must keep the multicast mapping alive until the stream has passed the call.  No
+ * counterpart in the reference (one GPU: src/gemm/benchmark.cc:54). */
+int mmbo_gemm_f16_mcast(int transA, int transB, size_t m, size_t n, size_t k, const float* alpha,
+                        const void* A, size_t lda, const void* B, size_t ldb, const float* beta,
+                        void* C, size_t ldc, void* C_multicast, int kernelId, void* stream);
+
+/* One GEMM sharded over the GPUs of a node by column blocks of op(B) and C (new capability: the
+ * reference drives one GPU, device index fixed, src/gemm/benchmark.cc:54).  One process per GPU;
+ * every rank calls with the same m, n, k (the WHOLE problem) and its own rank.  Rank r owns the
+ * columns mmbo_shard_columns(n, nGpus, r, 256) gives.  A (all of it) and C (the whole m x n
+ * matrix, ldc) are this GPU's; B_block is this rank's block of op(B): k x ncols (ldb >= k) for
+ * transB == 0, ncols x k (ldb >= ncols) for transB != 0.  The rank computes its block of C in
+ * place; there is no communication in the contraction.  gatherC != 0: afterwards the blocks are
+ * exchanged with NCCL on `stream` (ncclAllGather in place for equal blocks, a group of
+ * ncclBroadcast otherwise), so that every rank ends with the whole C; needs ldc == m.
+ * ncclComm is the caller's ncclComm_t for these nGpus ranks (may be NULL when gatherC == 0); the
+ * library looks NCCL up in the process at run time (MMBO_ERR_NO_NCCL if there is none) and checks
+ * that the communicator has nGpus ranks and this rank.  Collective when gatherC != 0: every rank
+ * must make the call, in the same order relative to its other NCCL calls. */
+int mmbo_gemm_f16_sharded(int nGpus, int rank, void* ncclComm, int gatherC, int transA, int transB,
+                          size_t m, size_t n, size_t k, const float* alpha, const void* A, size_t lda,
+                          const void* B_block, size_t ldb, const float* beta, void* C, size_t ldc,
+                          int kernelId, void* stream);
+
+/* The same with operands in HOST memory, for the round trip the reference's harness makes
+ * (src/gemm/benchmark.cc:57-63, src/gemm/test.cc:89).  A is the whole of A in host memory (every
+ * rank sees the same contents); B_block and C_block are this rank's column blocks (C_block: m x
+ * ncols, ldc).  Rank r copies only ITS share of A's stored columns to its GPU
+ * (mmbo_shard_columns(columns of the stored A, nGpus, r, 8)); the shares then travel between the
+ * GPUs over NVLink (ncclAllGather / grouped ncclBroadcast on an internal stream), so the host
+ * bridge carries A once per node instead of once per GPU.  B and C blocks go through the same
+ * overlapped panel pipeline as mmbo_gemm_f16_host.  Returns when C_block holds the result.
+ * Collective: every rank of the communicator must make the call. */
+int mmbo_gemm_f16_sharded_host(int nGpus, int rank, void* ncclComm, int transA, int transB, size_t m,
+                               size_t n, size_t k, const float* alpha, const void* A, size_t lda,
+                               const void* B_block, size_t ldb, const float* beta, void* C_block,
+                               size_t ldc, int kernelId);
 
 /* The same GEMMs on operands in HOST memory: A, B, C are host pointers (pinned memory
  * gives full copy bandwidth), everything else as above.  This is the whole round trip
@@ -116,8 +164,14 @@ int mmbo_gemm_f64_host(int transA, int transB, size_t m, size_t n, size_t k, con
 /* Strided-batched GEMM: problem b of `batch` uses A + b*strideA, B + b*strideB,
  * C + b*strideC (strides in elements).  The reference's Tensile argument block already
  * carries a batch index and these strides (strideC2K / strideA2K / strideB2K and sizeK,
- * src/gemm/gemm.h:62-69,88-92) with sizeK fixed to 1.  alpha and beta point to float for
- * f16/f32 and to double for f64.  The problems are queued one after another on `stream`. */
+ * src/gemm/gemm.h:62-69,88-92) with sizeK fixed to 1, and its kernel takes the problem
+ * index from the third grid dimension (src/gemm/ref/Kernels.cpp:254).  alpha and beta
+ * point to float for f16/f32 and to double for f64.  The whole batch is ONE launch: the
+ * problem index is a coordinate of the persistent tile walk (tensor-core kernels, 3-D
+ * tensor maps whose outermost dimension is the batch) or the third grid dimension (the
+ * other kernels).  Falls back to one call per problem only where a kernel cannot address
+ * the batch: fp16 operands that need realigning or strides that are not whole 16-byte
+ * units, fp32 row 6, more than 65535 problems. */
 int mmbo_gemm_strided_batched(int dtype, int transA, int transB, size_t m, size_t n, size_t k,
                               const void* alpha, const void* A, size_t lda, size_t strideA,
                               const void* B, size_t ldb, size_t strideB, const void* beta, void* C,
@@ -148,6 +202,30 @@ int mmbo_tuning_load(const char* path);
 void mmbo_tuning_clear(void);
 
 const char* mmbo_status_string(int status);
+
+/* Switches for experiments and diagnosis, by name:
+ *   "diag"          diagnostic kernels whose results are wrong by design (bit 0: no C store,
+ *                   bit 1: no accumulator drain) -- the counterpart of the reference's
+ *                   src/gemm/assembly/test_main_loop.s and error_kernel_000.s;
+ *   "wgm"           work-group-mapping width for every kernel (0 = each table row's own;
+ *                   the reference fixes 8: src/gemm/ref/Kernels.cpp:209);
+ *   "tf32_chunk"    stages per tensor-memory accumulation chain of the 3xTF32 kernels;
+ *   "f32_exact"     non-zero: automatic fp32 selection never takes a split-precision row,
+ *                   tuned rows included;
+ *   "dgemm_stage_c" 64-row fp64 tiles stage the old C through shared memory (default 1);
+ *   "split_k"       0 automatic, 1 never split the contraction, n > 1 force n slices.
+ * Initial values come from the environment variables MMBO_DIAG, MMBO_WGM, MMBO_TF32_CHUNK,
+ * MMBO_F32_EXACT, MMBO_DGEMM_STAGE_C, MMBO_SPLIT_K, which are read once, when the first
+ * call needs a setting; later changes of the environment have no effect.  (The reference has
+ * compile-time #defines only: src/gemm/benchmark.cc:7-14.) */
+int mmbo_set_option(const char* name, unsigned int value);
+int mmbo_get_option(const char* name, unsigned int* value);
+
+/* Number of kernel launches this library has queued since it was loaded (GEMM, split and
+ * scale kernels; not the operand generator).  For tests and benchmarks that state how many
+ * launches a call costs (the reference launches exactly one kernel per call:
+ * src/gemm/driver.h:56-59). */
+unsigned long long mmbo_launch_count(void);
 
 /* Tile rasterisation used by the kernels (the reference's work-group mapping,
  * src/gemm/ref/Kernels.cpp:209-236), exposed for host-side checks. */

@@ -62,7 +62,17 @@ inline int launchGemm(int dtype, int transA, int transB, size_t m, size_t n, siz
                          static_cast<const float*>(B), ldb, beta, static_cast<float*>(C), ldc, kernelId, stream);
   if (dtype == MMBO_DTYPE_F16)
     return mmbo_gemm_f16(transA, transB, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, kernelId, stream);
-  return MMBO_ERR_BAD_DTYPE;
+  return MMBO_ERR_BAD_DTYPE;  // binary64 takes double scalars: the overload below
+}
+
+// The same entry for binary64, the reference's own data type (its launchGemm is what
+// dgemm_NT calls: src/gemm/gemm.h:95): the scalars are double, as in the reference.
+inline int launchGemm(int dtype, int transA, int transB, size_t m, size_t n, size_t k, const double* alpha,
+                      const void* A, size_t lda, const void* B, size_t ldb, const double* beta, void* C,
+                      size_t ldc, int kernelId = MMBO_KERNEL_AUTO, cudaStream_t stream = nullptr) {
+  if (dtype != MMBO_DTYPE_F64) return MMBO_ERR_BAD_DTYPE;  // fp32 / fp16 take float scalars
+  return mmbo_gemm_f64(transA, transB, m, n, k, alpha, static_cast<const double*>(A), lda,
+                       static_cast<const double*>(B), ldb, beta, static_cast<double*>(C), ldc, kernelId, stream);
 }
 
 }  // namespace mmbo

@@ -62,7 +62,7 @@ def test_shard_columns_rejects(mm):
 
 def test_status_strings(mm):
     assert mm.status_string(0) == "ok"
-    for code in range(-17, 0):
+    for code in range(-20, 0):
         assert mm.status_string(code) not in ("", "unknown status")
 
 
@@ -145,3 +145,44 @@ def test_fp64_selection_is_the_warp_specialised_tensor_kernel():
     assert "dmma_ws_MT128x064" in name(4096, 4096, 4096)
     assert "dmma_ws_MT128x064" in name(2176, 2176, 2176)   # 578 tiles of 128 rows: 1.95 rounds of 296 slots
     assert "dmma_ws_MT064x064" in name(2368, 2368, 2368)   # 703 tiles would be 2.4 rounds; 1369 of 64 rows are 4.6
+
+
+def test_exact_fp32_switch_beats_tuned_tensor_rows(mm):
+    """With the exact-fp32 switch on, automatic selection never returns a split-precision
+    (tensor-core) row -- not from the heuristics and not from a tuned row, the packaged table
+    included.  Host-side decision: no GPU needed."""
+    import gemm_mmbo_b200._lib as L
+    mm.tuning_clear()
+    if L._TABLE.exists():
+        mm.tuning_load(L._TABLE)
+    mm.tuning_set("f32", False, True, 1536, 2048, 384, 5)
+    args = ("f32", False, True, 1536, 2048, 384, BAD, 1536, BAD, 2048, BAD, 1536)
+    try:
+        assert mm.get_option("f32_exact") == 0
+        assert mm.kernel_params("f32", mm.select_kernel(*args))["tensorCores"] == 1
+        mm.set_option("f32_exact", 1)
+        kid = mm.select_kernel(*args)
+        assert mm.kernel_params("f32", kid)["tensorCores"] == 0, kid
+        big = ("f32", False, False, 8192, 8192, 8192, BAD, 8192, BAD, 8192, BAD, 8192)
+        assert mm.kernel_params("f32", mm.select_kernel(*big))["tensorCores"] == 0
+    finally:
+        mm.set_option("f32_exact", 0)
+        mm.tuning_clear()
+    with pytest.raises(mm.MmboError) as e:
+        mm.set_option("no_such_switch", 1)
+    assert e.value.status == -18
+
+
+def test_strided_batched_rejects_bad_arguments(mm):
+    from gemm_mmbo_b200._lib import LIB
+    one = ctypes.c_float(1.0)
+    a = ctypes.cast(ctypes.byref(one), ctypes.c_void_p)
+    ok = [1, 0, 1, 64, 32, 16, a, BAD, 64, 64 * 16, BAD, 32, 32 * 16, a, BAD, 64, 64 * 32, 4, -1, None]
+    bad = list(ok); bad[0] = 7
+    assert LIB.mmbo_gemm_strided_batched(*bad) == -9
+    bad = list(ok); bad[8] = 63
+    assert LIB.mmbo_gemm_strided_batched(*bad) == -4
+    bad = list(ok); bad[18] = 99
+    assert LIB.mmbo_gemm_strided_batched(*bad) == -7
+    bad = list(ok); bad[17] = 0  # an empty batch is accepted and launches nothing
+    assert LIB.mmbo_gemm_strided_batched(*bad) == 0

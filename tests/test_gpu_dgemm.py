@@ -35,28 +35,6 @@ def test_dgemm_reference_sweep_shape(cuda, mm, oracle):
     run_and_check(cuda, mm, case, -1)
 
 
-@pytest.mark.parametrize("dtype", ["f16", "f32", "f64"])
-def test_strided_batched(cuda, mm, oracle, dtype):
-    """Three problems packed back to back in one allocation each, through the batched entry."""
-    import numpy as np
-    from helpers import TOL
-    torch = cuda
-    m, n, k, batch = 136, 72, 200, 3
-    cases = [Case(oracle, dtype, False, True, m, n, k, 1.0, 0.5, seed=100 + b) for b in range(batch)]
-    tdt = {"f16": torch.float16, "f32": torch.float32, "f64": torch.float64}[dtype]
-    dA = torch.from_numpy(np.stack([c.A for c in cases])).cuda()
-    dB = torch.from_numpy(np.stack([c.B for c in cases])).cuda()
-    dC = torch.from_numpy(np.stack([c.C for c in cases])).cuda()
-    assert dA.dtype == tdt
-    mm.gemm_strided_batched(dtype, False, True, m, n, k, 1.0, dA, m, m * k, dB, n, n * k, 0.5, dC, m, m * n, batch)
-    torch.cuda.synchronize()
-    assert mm.device_status() == 0
-    out = dC.cpu().numpy()
-    for b, case in enumerate(cases):
-        err = oracle.rel_frobenius(dtype, m, n, np.ascontiguousarray(out[b]), m, case.reference())
-        assert err <= TOL[dtype], (b, err)
-
-
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_dgemm_persistent_kernel_many_tiles(cuda, mm, oracle, ta, tb):
     """More tiles than resident CTAs (each CTA walks several), ragged edges in m and n, a K tail

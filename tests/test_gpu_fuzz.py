@@ -8,10 +8,9 @@ from helpers import Case, run_and_check
 
 pytestmark = pytest.mark.gpu
 
-TABLE_SIZE = {"f16": 5, "f32": 6, "f64": 3}
 
 
-def _draw(rng, dtype):
+def _draw(rng, dtype, table_size):
     # extents: mostly small/ragged, sometimes a few tiles wide; log-uniform-ish
     def extent(hi):
         return int(min(hi, max(1, round(np.exp(rng.uniform(0.0, np.log(hi)))))))
@@ -28,15 +27,16 @@ def _draw(rng, dtype):
         pad = tuple(int((-x) % align + align * rng.integers(0, 3)) for x in lead_dims(ta, tb, m, n, k))
     alpha = float(rng.choice([1.0, -1.0, 0.5, 1.75]))
     beta = float(rng.choice([0.0, 1.0, -0.25, 0.5]))
-    kid = int(rng.integers(-1, TABLE_SIZE[dtype]))
+    kid = int(rng.integers(-1, table_size))  # -1 = automatic, else any row of the table
     return ta, tb, m, n, k, alpha, beta, pad, kid
 
 
 @pytest.mark.parametrize("dtype,seed,count", [("f16", 101, 60), ("f32", 202, 60), ("f64", 303, 30)])
 def test_random_cases(cuda, mm, oracle, dtype, seed, count):
     rng = np.random.default_rng(seed)
+    table_size = mm.num_kernels(dtype)
     for i in range(count):
-        ta, tb, m, n, k, alpha, beta, pad, kid = _draw(rng, dtype)
+        ta, tb, m, n, k, alpha, beta, pad, kid = _draw(rng, dtype, table_size)
         case = Case(oracle, dtype, ta, tb, m, n, k, alpha, beta, pad=pad, seed=seed * 1000 + i,
                     dist=oracle.DIST_NORMAL, scale=0.5, c_poison=(beta == 0.0))
         try:

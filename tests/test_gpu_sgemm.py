@@ -1,6 +1,7 @@
 """SGEMM parity: every fp32 kernel of the table (and automatic selection) against the
 oracle, relative Frobenius error <= 1e-5, all transpose modes, ragged shapes, padded
 leading dimensions, guard bands, beta == 0 with poisoned C."""
+import numpy as np
 import pytest
 
 from helpers import Case, run_and_check
@@ -92,6 +93,62 @@ def test_sgemm_lent_workspace(cuda, mm, oracle):
     finally:
         mm.set_workspace(None)
     run_and_check(cuda, mm, case, 3)  # library-managed scratch again
+
+
+def test_rejected_workspace_leaves_library_scratch_usable(cuda, mm, oracle):
+    """A misaligned buffer is refused (-15) before any state changes: the library's own scratch is
+    neither freed nor left dangling, and the next split-precision GEMM is still right."""
+    case = Case(oracle, "f32", False, True, 300, 200, 100, 1.5, -0.25, pad=(3, 3, 3))
+    ref = case.reference()
+    mm.set_workspace(None)
+    run_and_check(cuda, mm, case, 3, ref=ref)          # library-managed scratch now exists
+    junk = cuda.empty(1 << 20, dtype=cuda.uint8, device="cuda")
+    with pytest.raises(mm.MmboError) as e:
+        mm.set_workspace(junk.data_ptr() // 1024 * 1024 + 1024 + 8, 1 << 19)
+    assert e.value.status == -15
+    run_and_check(cuda, mm, case, 3, ref=ref)
+    run_and_check(cuda, mm, case, 5, ref=ref)
+
+
+def test_lent_workspace_too_small_falls_back_on_automatic_selection(cuda, mm, oracle):
+    """Automatic fp32 selection never fails for want of scratch: with a lent buffer that is too small
+    for the split-precision rows it takes a CUDA-core kernel; a forced row still reports -15."""
+    torch = cuda
+    m = n = k = 640  # 640^3 > 512^3: automatic selection would take a split-precision row
+    case = Case(oracle, "f32", False, False, m, n, k, 1.0, 0.0, c_poison=True)
+    buf = torch.empty(4096 + 1024, dtype=torch.uint8, device="cuda")
+    base = (buf.data_ptr() + 1023) // 1024 * 1024
+    try:
+        mm.set_workspace(base, 4096)
+        run_and_check(cuda, mm, case, -1)
+        with pytest.raises(mm.MmboError) as e:
+            run_and_check(cuda, mm, case, 4)
+        assert e.value.status == -15
+    finally:
+        mm.set_workspace(None)
+
+
+def test_two_streams_share_the_library_scratch_safely(cuda, mm, oracle):
+    """Default fp32 GEMMs (split-precision rows, which repack their operands into the one
+    library-managed scratch buffer) queued on two streams with different operands: the library orders
+    the scratch users on the GPU, so both results match the oracle."""
+    torch = cuda
+    cases = [Case(oracle, "f32", False, True, 768, 640, 700, 1.0, 0.5, seed=31),
+             Case(oracle, "f32", True, False, 704, 832, 650, -1.0, 0.0, seed=32, c_poison=True)]
+    refs = [c.reference() for c in cases]
+    dev = [[torch.from_numpy(x).cuda() for x in (c.A, c.B, c.C)] for c in cases]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for rep in range(4):  # several rounds, alternating streams, nothing in between
+        for c, (dA, dB, dC), st in zip(cases, dev, streams):
+            if rep:
+                dC.copy_(torch.from_numpy(c.C), non_blocking=False)
+            mm.gemm("f32", c.ta, c.tb, c.m, c.n, c.k, c.alpha, dA, c.lda, dB, c.ldb, c.beta, dC, c.ldc, -1, st)
+    torch.cuda.synchronize()
+    assert mm.device_status() == 0
+    for c, (dA, dB, dC), ref in zip(cases, dev, refs):
+        err = oracle.rel_frobenius("f32", c.m, c.n, np.ascontiguousarray(dC.cpu().numpy()), c.ldc, ref)
+        assert err <= 1e-5, err
 
 
 @pytest.mark.parametrize("ta,tb", MODES)

@@ -39,13 +39,18 @@ def test_noalloc_matches_existing_entry_point_twice_in_a_row(cuda, mm, oracle):
     from gemm_mmbo_b200._lib import LIB
     calls = [Case(oracle, "f32", False, True, 520, 392, 328, 1.5, -0.25, pad=(3, 3, 3), seed=11),
              Case(oracle, "f32", True, False, 300, 777, 1000, 1.0, 0.0, pad=(0, 4, 1), seed=12, c_poison=True)]
+    free_after = []
     for case in calls:
         _, dA = to_device(torch, case.A)
         _, dB = to_device(torch, case.B)
         _, dC_new = to_device(torch, case.C)
         _, dC_old = to_device(torch, case.C)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = _noalloc(LIB, case, dA, dB, dC_new)
         assert rc == 0, mm.status_string(rc)
+        torch.cuda.synchronize()
+        free_after.append((free_before, torch.cuda.mem_get_info()[0]))
         mm.gemm("f32", case.ta, case.tb, case.m, case.n, case.k, case.alpha, dA, case.lda, dB, case.ldb, case.beta,
                 dC_old, case.ldc, 4)
         torch.cuda.synchronize()
@@ -61,6 +66,11 @@ def test_noalloc_matches_existing_entry_point_twice_in_a_row(cuda, mm, oracle):
             assert np.array_equal(new[:, case.m:].view(np.uint32), case.C[:, case.m:].view(np.uint32))
         err = oracle.rel_frobenius("f32", case.m, case.n, np.ascontiguousarray(new), case.ldc, case.reference())
         assert err <= TOL, err
+    # The property in the name: free device memory is the same before and after a call.  The very
+    # first call of a process may make the driver load the kernels' code, so it is the second
+    # (warm) call that is held to it.
+    before, after = free_after[1]
+    assert after == before, f"device memory changed across a warm call: {before} -> {after}"
 
 
 def test_noalloc_refuses_problems_beyond_its_scratch(cuda, mm):
