@@ -52,6 +52,8 @@ SIGNATURES = {
                                           _vp, _sz, _vp, _sz]),
     "mmbo_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "mmbo_tuning_set": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, ctypes.c_int]),
+    "mmbo_tuning_set_split": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, ctypes.c_int,
+                                             ctypes.c_int]),
     "mmbo_tuning_load": (ctypes.c_int, [ctypes.c_char_p]),
     "mmbo_tuning_clear": (None, []),
     "mmbo_wgm_map": (None, [ctypes.c_uint32] * 5 + [_u32p, _u32p]),

@@ -22,13 +22,27 @@ def problems(presets: list[str]):
         out += [("f32", "NN", 1024, 1024, 1024), ("f16", "NT", 8192, 8192, 8192)]
         out += [("f32", t, 4095, 4097, 1023) for t in ("NN", "NT", "TN", "TT")]
         out += [("f16", "TN", 65536, 128, 4096), ("f16", "TN", 128, 65536, 4096), ("f16", "TN", 8192, 8192, 256)]
+    if "square" in presets:  # medium squares, where the tile count rarely fills whole rounds of the CTA slots
+        for dtype in ("f16", "f32", "f64"):
+            out += [(dtype, "NT", s, s, s) for s in (1024, 1536, 2048, 2368, 3072)]
     if "sweep" in presets:  # the reference's run.sh sweep (M = 44160 .. 384 step -384, N = 2048, K = 384), thinned
         for dtype in ("f16", "f32", "f64"):
             out += [(dtype, "NT", m, 2048, 384) for m in (44160, 33408, 22272, 11136, 5376, 1536, 384)]
     return out
 
 
-def time_kernel(mm, torch, dtype, trans, m, n, k, kid, iters):
+SPLIT_ROWS = {"f64": (3, 4), "f32": (6,)}  # rows whose contraction can be split (stream-K)
+
+
+def time_kernel(mm, torch, dtype, trans, m, n, k, kid, iters, split=0):
+    mm.set_option("split_k", split)
+    try:
+        return _time_kernel(mm, torch, dtype, trans, m, n, k, kid, iters)
+    finally:
+        mm.set_option("split_k", 0)
+
+
+def _time_kernel(mm, torch, dtype, trans, m, n, k, kid, iters):
     ta, tb = trans[0] == "T", trans[1] == "T"
     tdt = {"f16": torch.float16, "f32": torch.float32, "f64": torch.float64}[dtype]
     ra, rb = (k if ta else m), (n if tb else k)
@@ -58,7 +72,7 @@ def time_kernel(mm, torch, dtype, trans, m, n, k, kid, iters):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", required=True)
-    ap.add_argument("--preset", default="baseline,sweep")
+    ap.add_argument("--preset", default="baseline,sweep,square")
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     import torch
@@ -67,25 +81,30 @@ def main() -> None:
     torch.cuda.set_device(0)
     mm.tuning_clear()
     lines = [f"# tuning table written by gemm_mmbo_b200.autotune on {torch.cuda.get_device_name(0)}, "
-             f"{time.strftime('%Y-%m-%d')}", "# dtype trans m n k kernelId   # best TFLOP/s (runner-up id: TFLOP/s)"]
+             f"{time.strftime('%Y-%m-%d')}",
+             "# dtype trans m n k kernelId [split: 1 never, 2 always]   # best TFLOP/s (heuristic id: TFLOP/s)"]
     for (dtype, trans, m, n, k) in problems(args.preset.split(",")):
         results = []
         for kid in range(mm.num_kernels(dtype)):
             if kid == 0 and 2.0 * m * n * k > 2e11:
                 continue  # the one-thread-per-element kernel is only a candidate for tiny problems
-            ms = time_kernel(mm, torch, dtype, trans, m, n, k, kid, args.iters)
-            if ms is not None:
-                results.append((2.0 * m * n * k / ms / 1e9, kid))
+            for split in ((1, 2) if kid in SPLIT_ROWS.get(dtype, ()) else (0,)):
+                ms = time_kernel(mm, torch, dtype, trans, m, n, k, kid, args.iters, split)
+                if ms is not None:
+                    results.append((2.0 * m * n * k / ms / 1e9, kid, split))
         results.sort(reverse=True)
         best = results[0]
         # a row is written only where measurement beats the built-in heuristic by more than 2 %
         ta, tb = trans[0] == "T", trans[1] == "T"
         heur = mm.select_kernel(dtype, ta, tb, m, n, k, 4096, (k if ta else m), 4096, (n if tb else k), 4096, m)
-        heur_tf = dict((kid, tf) for tf, kid in results).get(heur, 0.0)
-        if best[1] != heur and best[0] > 1.02 * heur_tf:
-            lines.append(f"{dtype} {trans} {m} {n} {k} {best[1]}   # {best[0]:.1f} (heuristic {heur}: {heur_tf:.1f})")
+        heur_ms = time_kernel(mm, torch, dtype, trans, m, n, k, heur, args.iters, 0)  # the library's own split decision
+        heur_tf = 2.0 * m * n * k / heur_ms / 1e9 if heur_ms else 0.0
+        if best[0] > 1.02 * heur_tf:
+            split = f" {best[2]}" if best[2] else ""
+            lines.append(f"{dtype} {trans} {m} {n} {k} {best[1]}{split}   # {best[0]:.1f} (heuristic {heur}: {heur_tf:.1f})")
         else:
-            lines.append(f"# {dtype} {trans} {m} {n} {k}: heuristic {heur} kept ({heur_tf:.1f}; best {best[1]}: {best[0]:.1f})")
+            lines.append(f"# {dtype} {trans} {m} {n} {k}: heuristic {heur} kept ({heur_tf:.1f}; best {best[1]}"
+                         f"{' split ' + str(best[2]) if best[2] else ''}: {best[0]:.1f})")
         print(lines[-1], flush=True)
     out = pathlib.Path(args.out)
     out.parent.mkdir(parents=True, exist_ok=True)

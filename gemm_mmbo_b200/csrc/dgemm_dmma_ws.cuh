@@ -38,6 +38,7 @@
 #include "dgemm_dmma.cuh"  // dmma_m8n8k4, DgemmParams
 #include "ptx.cuh"
 #include "raster.h"
+#include "stream_k.cuh"
 
 namespace mmbo {
 
@@ -125,11 +126,11 @@ __device__ __forceinline__ void ws_fill_elements(uint32_t slab, const double* __
   }
 }
 
-template <bool TRANS_A, bool TRANS_B, int BM>
+template <bool TRANS_A, bool TRANS_B, int BM, bool SK = false>
 __global__ void __launch_bounds__(kWsThreads, 2)
 dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_c, const double* __restrict__ A, const double* __restrict__ B, double* __restrict__ C,
-                     const DgemmParams p) {
+                     const DgemmParams p, const StreamK sk) {
   constexpr bool A_KMAJOR = TRANS_A, B_KMAJOR = !TRANS_B;  // which index is contiguous in memory
   using T = WsTile<BM, A_KMAJOR, B_KMAJOR>;
   using SA = typename T::SA;
@@ -180,20 +181,26 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
     const int pw = warp - kWsConsumers;
     if (solo && pw != 0) return;
-    // the epilogue's C lines are requested from L2 this many slabs before the tile's last one
-    const uint32_t c_prefetch_kb = num_kb > 24u ? num_kb - 24u : 0u;
     uint32_t issued = 0, c_phase = 0;
     bool ok = true, c_in_flight = false;
-    // The staged C of a tile is requested a few slabs into the tile: by then the consumers are past
-    // the previous tile's epilogue, so the wait for the buffer does not hold up the slab ring.
-    const uint32_t c_stage_kb = num_kb > 4u ? 4u : num_kb - 1u;
-    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+    SkWalk<SK> walk;
+    walk.init(sk, num_tiles, num_kb);
+    uint32_t tile, kb0, kb1;
+    while (ok && walk.next(&tile, &kb0, &kb1)) {
       uint32_t tile_m, tile_n;
       const uint32_t prob = locate(tile, &tile_m, &tile_n);
       const uint32_t m0 = tile_m * BM, n0 = tile_n * kWsBN;
       const bool a_inside = m0 + BM <= p.m, b_inside = n0 + kWsBN <= p.n;
-      for (uint32_t kb = 0; kb < num_kb; ++kb) {
-        if (stage_c && pw == 0 && kb == c_stage_kb) {
+      // Only the CTA that holds a tile's first slabs applies alpha / beta and touches C (always, when the
+      // contraction is not split).  The epilogue's C lines are requested from L2 24 slabs before the
+      // item's last one; the staged C a few slabs into the item: by then the consumers are past the
+      // previous tile's epilogue, so the wait for the buffer does not hold up the slab ring.
+      const bool epilogue_here = kb0 == 0u;
+      const uint32_t len = kb1 - kb0;
+      const uint32_t c_prefetch_kb = len > 24u ? kb1 - 24u : kb0;
+      const uint32_t c_stage_kb = kb0 + (len > 4u ? 4u : len - 1u);
+      for (uint32_t kb = kb0; kb < kb1; ++kb) {
+        if (stage_c && epilogue_here && pw == 0 && kb == c_stage_kb) {
           if (!mbar_wait(smem_u32(&c_empty_bar), c_phase ^ 1u, &abort_flag, kFaultWaitCLoad, 0)) {
             ok = false;
             break;
@@ -205,7 +212,7 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           c_in_flight = true;
           c_phase ^= 1u;
         }
-        if (p.beta != 0.0 && !stage_c && kb == c_prefetch_kb) {
+        if (p.beta != 0.0 && !stage_c && epilogue_here && kb == c_prefetch_kb) {
           // Ask L2 for this tile's C: a bulk prefetch (the 1-D form of the TMA prefetch) per column
           // where the column pieces are 16-byte aligned, else one prefetch per 128-byte line.
           const uint32_t rows = p.m - m0 < (uint32_t)BM ? p.m - m0 : (uint32_t)BM;
@@ -289,7 +296,11 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int wm = (warp & 1) * (BM / 2), wn = (warp >> 1) * 32;  // this warp's (BM / 2) x 32 piece of the tile
   const double alpha = p.alpha, beta = p.beta;
   uint32_t c_phase = 0;
-  for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+  SkWalk<SK> walk;
+  walk.init(sk, num_tiles, num_kb);
+  uint32_t tile, kb0, kb1;
+  constexpr uint32_t kAccPerThread = kFragM * 8;  // accumulator doubles of one consumer thread
+  while (walk.next(&tile, &kb0, &kb1)) {
     uint32_t tile_m, tile_n;
     const uint32_t prob = locate(tile, &tile_m, &tile_n);
     double* __restrict__ Cp = C + (size_t)prob * p.batch_c;
@@ -300,7 +311,7 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
 
-    for (uint32_t kb = 0; kb < num_kb; ++kb) {
+    for (uint32_t kb = kb0; kb < kb1; ++kb) {
       if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag, kFaultWaitFull, stage)) return;
       // element (row, k) of a slab: SA::at / SB::at; this lane's fragments start at (w + gid, tig)
       const double* __restrict__ a_s = ws_smem + stage * SA::kDoubles + SA::at(wm + gid, tig);
@@ -320,6 +331,47 @@ dgemm_dmma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
       if (++stage == kStages) { stage = 0; phase ^= 1u; }
+    }
+
+    if (SK && kb0 != 0u) {
+      // A later piece of a tile whose first slabs another CTA holds: hand the partial sums over
+      // (value v of thread t at [(cta * N + v) * 128 + t]; the owner's thread t reads them back),
+      // then raise this warp's flag.
+      double* part = static_cast<double*>(sk.partials) + (size_t)blockIdx.x * kAccPerThread * 128u + tid;
+#pragma unroll
+      for (int i = 0; i < kFragM; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __stcg(part + (size_t)((i * 4 + j) * 2 + 0) * 128u, acc[i][j][0]);
+          __stcg(part + (size_t)((i * 4 + j) * 2 + 1) * 128u, acc[i][j][1]);
+        }
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) sk_store_flag(sk.flags + blockIdx.x * kWsConsumers + warp, sk.epoch);
+      continue;
+    }
+    if (SK && kb1 != num_kb) {
+      // First slabs of a tile that continues in the next CTAs' runs (each reaches its piece first
+      // thing): add their partial sums in CTA order, then finish the tile here.
+      const unsigned long long units = (unsigned long long)num_tiles * num_kb;
+      uint32_t have = kb1, j = blockIdx.x + 1u;
+      while (have < num_kb && j < gridDim.x) {
+        const unsigned long long run = sk_first_unit(units, j + 1u, gridDim.x) - sk_first_unit(units, j, gridDim.x);
+        const uint32_t piece = run < (unsigned long long)(num_kb - have) ? (uint32_t)run : num_kb - have;
+        if (piece != 0u) {
+          if (!sk_wait_flag(sk.flags + j * kWsConsumers + warp, sk.epoch, &abort_flag, j)) return;
+          const double* part = static_cast<const double*>(sk.partials) + (size_t)j * kAccPerThread * 128u + tid;
+#pragma unroll
+          for (int i = 0; i < kFragM; ++i)
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              acc[i][jj][0] += __ldcg(part + (size_t)((i * 4 + jj) * 2 + 0) * 128u);
+              acc[i][jj][1] += __ldcg(part + (size_t)((i * 4 + jj) * 2 + 1) * 128u);
+            }
+        }
+        have += piece;
+        ++j;
+      }
     }
 
     // accumulator (i, j): C[m = gid][n = 2*tig + {0, 1}] of the 8 x 8 block at (wm + 8i, wn + 8j).

@@ -55,7 +55,10 @@ constexpr int kEpiBufBytes = 32 * 128;  // 32 C columns x 64 rows of fp16, per w
 // half (TM / 2 rows) of op(A).
 // EW = epilogue warps: 4 (one per 32-lane quarter of tensor memory) or 8 (two per
 // quarter, each taking half of the accumulator's columns).
-template <int TM, int STAGES, int CG = 1, int EW = 4>
+// CSETS = sets of staging buffers per epilogue warp: 2 lets the old C of the next tile be requested a tile
+// ahead (shared memory that then cannot hold operand stages), 1 keeps two buffers per warp and relies on
+// an L2 prefetch of the next tile's C.
+template <int TM, int STAGES, int CG = 1, int EW = 4, int CSETS = (EW == 8 ? 2 : 1)>
 struct HgemmSmem {
   static constexpr int kThreads = 64 + 32 * EW;
   static constexpr int kAopRows = TM / CG;                // rows of op(A) staged by one CTA
@@ -66,12 +69,15 @@ struct HgemmSmem {
   // Staging buffers per epilogue warp: two; with 8 epilogue warps (at most two chunks per warp
   // and tile) two sets of two, so that the old C of the next tile can be requested a whole
   // tile ahead while this tile's set is still in use.
-  static constexpr int kCSets = EW == 8 ? 2 : 1;
+  static constexpr int kCSets = CSETS;
   static constexpr int kBufsPerWarp = 2 * kCSets;
   static constexpr int kEpiBytes = EW * kBufsPerWarp * kEpiBufBytes;
   static constexpr int kBarOffset = kEpiOffset + kEpiBytes;
-  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], cload[EW][kBufsPerWarp]
-  static constexpr int kNumBars = 2 * STAGES + 4 + kBufsPerWarp * EW;
+  // Accumulators in tensor memory (512 columns): two of 256 columns, or four of 128 -- with short
+  // contractions the deeper queue keeps the UMMA issuer from ever waiting for the epilogue.
+  static constexpr int kAccs = 512 / TM;
+  // full[STAGES], empty[STAGES], tmem_full[kAccs], tmem_empty[kAccs], cload[EW][kBufsPerWarp]
+  static constexpr int kNumBars = 2 * STAGES + 2 * kAccs + kBufsPerWarp * EW;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
   static constexpr int kTotal = kMiscOffset + 16;
   static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024 bytes
@@ -129,20 +135,21 @@ __device__ __forceinline__ void trace_stamp(unsigned long long* trace, uint32_t 
   if (trace != nullptr && blockIdx.x == 0 && tile_slot < 64u) trace[tile_slot * 16u + ev] = clock64();
 }
 
-template <int TM, int STAGES, bool A_KMAJOR, bool B_KMAJOR, int CG = 1, int EW = 4>
+template <int TM, int STAGES, bool A_KMAJOR, bool B_KMAJOR, int CG = 1, int EW = 4, int CSETS = (EW == 8 ? 2 : 1)>
 __global__ void __launch_bounds__(64 + 32 * EW, 1)
 hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_c, const HgemmParams p,
                      const __grid_constant__ HgemmPeerMaps peers) {
-  using L = HgemmSmem<TM, STAGES, CG, EW>;
+  using L = HgemmSmem<TM, STAGES, CG, EW, CSETS>;
   static_assert(TM == 128 || TM == 256, "TM is the UMMA N extent");
   static_assert(EW == 4 || EW == 8, "one or two epilogue warps per tensor-memory quarter");
   // 64-row chunks of the accumulator each epilogue warp drains per tile
   constexpr uint32_t kChunksPerWarp = (TM / 64) / (EW / 4);
   static_assert(kChunksPerWarp >= 1, "tile too narrow for this many epilogue warps");
   static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair per UMMA");
-  constexpr uint32_t kTmemCols = 2 * TM;
+  constexpr uint32_t kAccs = L::kAccs;
+  constexpr uint32_t kTmemCols = kAccs * TM;  // = 512: all of tensor memory
   // CTA pair: rank 0 (the leader) issues every UMMA and owns the barriers that count
   // both CTAs' copies; this CTA's index among the tile walkers is its cluster's index.
   const uint32_t cta_rank = (CG == 2) ? cluster_cta_rank() : 0u;
@@ -157,8 +164,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
   auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
   auto tmem_full_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
-  auto tmem_empty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
-  auto cload_bar = [&](uint32_t w, uint32_t b) { return bar_base + 8u * (2 * STAGES + 4 + L::kBufsPerWarp * w + b); };
+  auto tmem_empty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + kAccs + a); };
+  auto cload_bar = [&](uint32_t w, uint32_t b) { return bar_base + 8u * (2 * STAGES + 2 * kAccs + L::kBufsPerWarp * w + b); };
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOffset);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOffset + 4);
 
@@ -170,7 +177,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // tile id of the walk -> (tile row, tile column, problem of the batch)
   const bool batched = p.batch > 1u;  // 3-D tensor maps; single problems keep the 2-D forms
   auto locate = [&](uint32_t tile, uint32_t* tm, uint32_t* tn) -> uint32_t {
-    const uint32_t prob = tile / tiles_per_problem;
+    const uint32_t prob = batched ? tile / tiles_per_problem : 0u;  // (no division on the single-problem path)
     mmbo_tile_from_serial(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, p.wgm, tm, tn);
     return prob;
   };
@@ -182,7 +189,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (uint32_t a = 0; a < 2; ++a) {
+    for (uint32_t a = 0; a < kAccs; ++a) {
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), EW * CG);
     }
@@ -283,8 +290,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t stage = 0, phase = 0, local_tile = 0;
       bool ok = true;
       for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers, ++local_tile) {
-        const uint32_t acc = local_tile & 1u;
-        const uint32_t acc_phase = (local_tile >> 1) & 1u;
+        const uint32_t acc = local_tile % kAccs;
+        const uint32_t acc_phase = (local_tile / kAccs) & 1u;
         trace_stamp(p.trace, local_tile, 8);
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, kFaultWaitTmemEmpty, acc)) {
           ok = false;
@@ -345,43 +352,55 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // the set tile i - 1 used), so that its HBM latency hides behind a whole tile.
     constexpr bool kCAhead = L::kCSets == 2;
     static_assert(!kCAhead || kChunksPerWarp <= 2, "C one tile ahead needs a buffer per chunk");
+    // The warp's staging buffers form kSets sets of kSetChunks (one per chunk of a tile); tile i uses set
+    // i % kSets.  With several sets the old C of tile i + kSets - 1 is requested during tile i (into the set
+    // tile i - 1 used), so that its HBM latency hides behind kSets - 1 whole tiles: one tile ahead with
+    // 256-row tiles (two sets of two), three tiles ahead with 128-row tiles (four sets of one).
+    constexpr uint32_t kSetChunks = kChunksPerWarp < 2u ? kChunksPerWarp : 2u;
+    constexpr uint32_t kSets = kCAhead ? (uint32_t)L::kBufsPerWarp / kSetChunks : 1u;
+    constexpr uint32_t kAhead = kSets - 1u;
+    constexpr int kStoresPending = (int)(kSets * kSetChunks) - 1;  // bulk groups that may still be reading other buffers
     uint32_t c_in_flight = 0;  // bit b: a load into buffer b of this warp has been requested and not yet awaited
     auto request_c = [&](uint32_t t, uint32_t set) {  // whole warp; lane 0 issues: chunks of tile t into buffer set `set`
       uint32_t tm, tn;
       const int32_t pr = static_cast<int32_t>(locate(t, &tm, &tn));
       const uint32_t mr = tm * TM + col_base, nc = (tn * CG + cta_rank) * kTileN + 32u * q;
 #pragma unroll
-      for (uint32_t c = 0; c < (kChunksPerWarp < 2u ? kChunksPerWarp : 2u); ++c) {
+      for (uint32_t c = 0; c < kSetChunks; ++c) {
         const uint32_t mrow0 = mr + 64u * c;
         if (mrow0 < p.m && nc < p.n) {
-          c_in_flight |= 1u << (2u * set + c);
+          c_in_flight |= 1u << (kSetChunks * set + c);
           if (lane == 0) {
-            mbar_expect_tx(cload_bar(epi_w, 2u * set + c), kEpiBufBytes);
-            tma_load_tile(batched, warp_buf_base + (2u * set + c) * kEpiBufBytes, &tmap_c, cload_bar(epi_w, 2u * set + c),
+            mbar_expect_tx(cload_bar(epi_w, kSetChunks * set + c), kEpiBufBytes);
+            tma_load_tile(batched, warp_buf_base + (kSetChunks * set + c) * kEpiBufBytes, &tmap_c, cload_bar(epi_w, kSetChunks * set + c),
                         static_cast<int32_t>(mrow0), static_cast<int32_t>(nc), pr);
           }
         }
       }
     };
-    if (kCAhead && p.c_tma != 0u && use_c && walker < num_tiles) request_c(walker, 0u);
+    if (kCAhead && p.c_tma != 0u && use_c) {
+#pragma unroll
+      for (uint32_t a = 0; a < kAhead; ++a)
+        if (walker + a * num_walkers < num_tiles) request_c(walker + a * num_walkers, a);
+    }
     for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers, ++local_tile) {
       uint32_t tm_idx, tn_idx;
       const int32_t prob = static_cast<int32_t>(locate(tile, &tm_idx, &tn_idx));
       __half* const c_plain = p.c + static_cast<size_t>(prob) * p.c_batch_stride;  // this problem's C (plain epilogue)
       const uint32_t m0 = tm_idx * TM + col_base;
       const uint32_t ncol0 = (tn_idx * CG + cta_rank) * kTileN + 32u * q;  // first C column of this warp
-      const uint32_t acc = local_tile & 1u;
-      const uint32_t acc_phase = (local_tile >> 1) & 1u;
+      const uint32_t acc = local_tile % kAccs;
+      const uint32_t acc_phase = (local_tile / kAccs) & 1u;
       // Staging tile b (two per warp): row t = C column ncol0 + t, 64 fp16 = C rows of one
       // chunk; the 16-byte piece j of a row lives at piece j ^ (t & 7) (128-byte TMA swizzle).
       // With beta != 0 the old C of the first two chunks is requested now, before the wait
       // for the accumulator, so that its latency overlaps the main loop of this tile.
       const bool tracer = (warp == 2u && lane == 0u);
       if (tracer) trace_stamp(p.trace, local_tile, 0);
-      // buffer set of this tile (always 0 unless C is requested one tile ahead)
-      const uint32_t set = (kCAhead && c_tma && use_c) ? (local_tile & 1u) : 0u;
-      const uint32_t buf_base = warp_buf_base + 2u * set * kEpiBufBytes;
-      uint8_t* buf_gen = warp_buf_gen + 2u * set * kEpiBufBytes;
+      // buffer set of this tile
+      const uint32_t set = (kCAhead && c_tma) ? local_tile % kSets : 0u;
+      const uint32_t buf_base = warp_buf_base + kSetChunks * set * kEpiBufBytes;
+      uint8_t* buf_gen = warp_buf_gen + kSetChunks * set * kEpiBufBytes;
       if (!kCAhead && c_tma && use_c) {
         if (lane == 0) tma_store_wait_read<0>();  // the previous tile's stores have read their buffers
         __syncwarp();
@@ -399,10 +418,9 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (nm0 + 64u * c < p.m && nn0 < p.n)
             tma_prefetch_l2_tile(batched, &tmap_c, static_cast<int32_t>(nm0 + 64u * c), static_cast<int32_t>(nn0), npr);
       }
-      // Every lane polls; the outcome is made warp-uniform so that the aligned
-      // tcgen05 instructions below always run with a converged warp.
-      ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag,
-                                             kFaultWaitTmemFull, acc));
+      // One lane polls (with back-off once the wait has become a long one); the outcome is warp-uniform so
+      // that the aligned tcgen05 instructions below always run with a converged warp.
+      ok = mbar_wait_warp(tmem_full_bar(acc), acc_phase, abort_flag, kFaultWaitTmemFull, acc);
       if (!ok) break;
       if (tracer) trace_stamp(p.trace, local_tile, 2);
       tcgen05_fence_after();
@@ -416,10 +434,14 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           else mbar_arrive(tmem_empty_bar(acc));
         }
       };
-      // With at most 128 accumulator columns per warp the whole share is pulled into
-      // registers first and the accumulator handed back at once: for short contractions
-      // the time an accumulator stays occupied bounds the kernel.
+      // With at most 128 accumulator columns per warp the whole share is pulled into registers (no
+      // register buffer is reused within a tile) and the accumulator handed back at once.  Tensor-memory
+      // loads are slow -- about ten cycles per register and warp, and the warps of one scheduler share
+      // its port (measured: 1340 cycles for 128 columns, with or without UMMAs running).
       constexpr bool kEarlyDrain = kChunksPerWarp <= 2;
+      // (Measured on 44160 x 2048 x 384: 121 us with the split against 106 us without: the loads of the second
+      // half do not progress while the warp works on the first, so the switch stays off.)
+      constexpr bool kSplitDrain = false;
       // Otherwise two register buffers of one chunk each: the tensor-memory loads of chunk
       // c + 1 are in flight while chunk c is scaled, converted and staged.
       uint32_t racc[kEarlyDrain ? 2 * kChunksPerWarp : 4][32];
@@ -433,23 +455,32 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       };
       if constexpr (kEarlyDrain) {
-#pragma unroll
-        for (uint32_t i = 0; i < 2 * kChunksPerWarp; ++i) {
+        auto load_piece = [&](uint32_t i) {
           if (drain) tmem_ld_32x32(t_warp + 32u * i, racc[i]);
           else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) racc[i][e] = 0u;
           }
+        };
+        if constexpr (kSplitDrain) {
+          load_piece(0);
+          load_piece(1);
+          tmem_ld_wait();
+          load_piece(2);  // in flight during chunk 0; awaited, and the accumulator released, before chunk 1
+          load_piece(3);
+        } else {
+#pragma unroll
+          for (uint32_t i = 0; i < 2 * kChunksPerWarp; ++i) load_piece(i);
+          tmem_ld_wait();
+          release_accumulator();
         }
-        tmem_ld_wait();
-        release_accumulator();
         if (tracer) trace_stamp(p.trace, local_tile, 3);
-        if (kCAhead && c_tma && use_c && tile + num_walkers < num_tiles) {
-          // The other buffer set was last read by the previous tile's stores, issued a drain
-          // ago: by now they have long left shared memory, so this wait does not stall.
+        if (kCAhead && c_tma && use_c && tile + kAhead * num_walkers < num_tiles) {
+          // The set tile i - 1 used was last read by that tile's stores, issued a drain ago: by now
+          // they have long left shared memory, so this wait does not stall.
           if (lane == 0) tma_store_wait_read<0>();
           __syncwarp();
-          request_c(tile + num_walkers, set ^ 1u);
+          request_c(tile + kAhead * num_walkers, (local_tile + kAhead) % kSets);
         }
       }
       if constexpr (!kEarlyDrain) load_chunk(0u, racc[0], racc[1]);
@@ -461,15 +492,21 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t mrow0 = m0 + 64u * c;
         const bool in_range = (mrow0 < p.m) && (ncol0 < p.n);  // warp-uniform
         const bool load_c = use_c && in_range;
+        if constexpr (kSplitDrain) {
+          if (c == 1u) {  // the second half of the accumulator is in registers now: hand it back
+            tmem_ld_wait();
+            release_accumulator();
+          }
+        }
         if (c_tma) {
           if (!use_c || c >= 2u) {
-            // The store issued from this buffer two chunks ago must have read it.
-            if (lane == 0) tma_store_wait_read<1>();
+            // The store last issued from this buffer (kStoresPending + 1 chunks ago) must have read it.
+            if (lane == 0) tma_store_wait_read<kStoresPending>();
             __syncwarp();
-            if (load_c) c_in_flight |= 1u << (2u * set + b);
+            if (load_c) c_in_flight |= 1u << (kSetChunks * set + b);
             if (load_c && lane == 0) {  // chunks beyond the two requested up front
-              mbar_expect_tx(cload_bar(epi_w, 2u * set + b), kEpiBufBytes);
-              tma_load_tile(batched, sbuf, &tmap_c, cload_bar(epi_w, 2u * set + b), static_cast<int32_t>(mrow0),
+              mbar_expect_tx(cload_bar(epi_w, kSetChunks * set + b), kEpiBufBytes);
+              tma_load_tile(batched, sbuf, &tmap_c, cload_bar(epi_w, kSetChunks * set + b), static_cast<int32_t>(mrow0),
                           static_cast<int32_t>(ncol0), prob);
             }
           }
@@ -493,11 +530,11 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         if (c_tma && load_c) {
-          if (!mbar_wait(cload_bar(epi_w, 2u * set + b), (cphase >> (2u * set + b)) & 1u, abort_flag, kFaultWaitCLoad,
-                         epi_w))
+          if (!mbar_wait(cload_bar(epi_w, kSetChunks * set + b), (cphase >> (kSetChunks * set + b)) & 1u, abort_flag,
+                         kFaultWaitCLoad, epi_w))
             ok = false;
-          cphase ^= 1u << (2u * set + b);
-          c_in_flight &= ~(1u << (2u * set + b));
+          cphase ^= 1u << (kSetChunks * set + b);
+          c_in_flight &= ~(1u << (kSetChunks * set + b));
         }
         if (tracer && c == 0) trace_stamp(p.trace, local_tile, 4);  // old C of chunk 0 has arrived
         // `ok` may differ between lanes only after a time-out, when the data is

@@ -51,6 +51,7 @@ static const KernelRow kF16Rows[] = {
     {"hgemm_tcgen05_MT128x128x64_S6_CG1_WG192_WGM08", 128, 128, 192, 64, 6, 1, 8, 1},
     {"hgemm_tcgen05_MT256x256x64_S6_CG2_WG192_WGM08", 256, 256, 192, 64, 6, 2, 8, 1},
     {"hgemm_tcgen05_MT256x256x64_S3_CG2_WG320_WGM08", 256, 256, 320, 64, 3, 2, 8, 1},
+    {"hgemm_tcgen05_MT256x256x64_S5_CG2_WG320_WGM08", 256, 256, 320, 64, 5, 2, 8, 1},
 };
 // fp64 rows (the reference's own dtype).
 static const KernelRow kF64Rows[] = {
@@ -270,225 +271,6 @@ __global__ void bounded_wait_selftest_kernel(unsigned long long limit_ns) {
 static unsigned long long* g_trace_buffer = nullptr;
 constexpr size_t kTraceWords = 64 * 16;
 
-// ------------------------------------------------------------------ launches ---------
-template <typename T>
-static int launch_simple(const GemmArgs& g, cudaStream_t st) {
-  const size_t gx = (g.m + 31) / 32, gy = (g.n + 7) / 8;
-  if (gy > 65535 || gx > 0x7fffffffull || g.batch > 65535) return MMBO_ERR_TOO_LARGE;
-  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch), block(32, 8);
-  gemm_simple_kernel<T><<<grid, block, 0, st>>>(g.transA, g.transB, g.m, g.n, g.k, g.alpha,
-                                                static_cast<const T*>(g.A), g.lda,
-                                                static_cast<const T*>(g.B), g.ldb, g.beta,
-                                                static_cast<T*>(g.C), g.ldc, g.sA, g.sB, g.sC);
-  MMBO_COUNT_LAUNCH();
-  return (int)cudaGetLastError();
-}
-
-template <typename T>
-static int launch_scale(const GemmArgs& g, cudaStream_t st) {
-  const size_t gx = (g.m + 31) / 32, gy = (g.n + 7) / 8;
-  if (gy > 65535 || gx > 0x7fffffffull || g.batch > 65535) return MMBO_ERR_TOO_LARGE;
-  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch), block(32, 8);
-  scale_c_kernel<T><<<grid, block, 0, st>>>(g.m, g.n, g.beta, static_cast<T*>(g.C), g.ldc, g.sC);
-  MMBO_COUNT_LAUNCH();
-  return (int)cudaGetLastError();
-}
-
-// FFMA kernel with a producer warpgroup: an operand goes through TMA when its tile rows are
-// contiguous in memory, its base 16-byte aligned and its leading dimension a multiple of 4.
-static int launch_sgemm_ffma_ws(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
-  SgemmParams p;
-  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
-  p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
-  p.alpha = g.alpha; p.beta = g.beta; p.wgm = wgm;
-  p.batch_a = p.batch_b = p.batch_c = 0;
-  p.vec_a = p.vec_b = 0;
-  p.vec_c = aligned16(g.C) && g.ldc % 4 == 0;
-  SgemmWsFlags f;
-  f.tma_a = !g.transA && aligned16(g.A) && g.lda % 4 == 0;
-  f.tma_b = g.transB && aligned16(g.B) && g.ldb % 4 == 0;
-  CUtensorMap ta, tb;
-  memset(&ta, 0, sizeof(ta));
-  memset(&tb, 0, sizeof(tb));
-  if (f.tma_a) {
-    const int rc = make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.A, g.m, g.k, g.lda, kFwBM + kFwPad, kFwBK,
-                               CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc) return rc;
-  }
-  if (f.tma_b) {
-    const int rc = make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.B, g.n, g.k, g.ldb, kFwBN + kFwPad, kFwBK,
-                               CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc) return rc;
-  }
-  const size_t tiles = ((g.m + kFwBM - 1) / kFwBM) * ((g.n + kFwBN - 1) / kFwBN);
-  if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-  // Eight CTAs per SM in the grid, two resident: as CTAs finish their few tiles the hardware starts the
-  // next ones, which balances the end of the launch (4096^3: 61.1 TFLOP/s against 52.3 with 2 per SM).
-  const unsigned grid = (unsigned)std::min(tiles, (size_t)8 * (size_t)sm_count());
-  const float* A = static_cast<const float*>(g.A);
-  const float* B = static_cast<const float*>(g.B);
-  float* C = static_cast<float*>(g.C);
-  auto launch = [&](auto kernel) -> int {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwSmemBytes);
-    if (e != cudaSuccess) return (int)e;
-    kernel<<<grid, kFwThreads, kFwSmemBytes, st>>>(ta, tb, A, B, C, p, f);
-    MMBO_COUNT_LAUNCH();
-    return (int)cudaGetLastError();
-  };
-  if (!g.transA && !g.transB) return launch(sgemm_ffma_ws_kernel<false, false>);
-  if (!g.transA && g.transB) return launch(sgemm_ffma_ws_kernel<false, true>);
-  if (g.transA && !g.transB) return launch(sgemm_ffma_ws_kernel<true, false>);
-  return launch(sgemm_ffma_ws_kernel<true, true>);
-}
-
-template <int BM, int BN, int TTM, int TTN>
-static int launch_sgemm_ffma(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
-  constexpr int BK = 16;
-  SgemmParams p;
-  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
-  p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
-  p.alpha = g.alpha; p.beta = g.beta; p.wgm = wgm;
-  p.batch_a = g.sA; p.batch_b = g.sB; p.batch_c = g.sC;
-  // 128-bit accesses: base and pitch 16-byte aligned, and the contiguous extent a
-  // multiple of 4 so that no vector straddles the matrix edge (every problem of a batch).
-  const bool batched = g.batch > 1;
-  const size_t a_contig = g.transA ? g.k : g.m, b_contig = g.transB ? g.n : g.k;
-  p.vec_a = aligned16(g.A) && g.lda % 4 == 0 && a_contig % 4 == 0 && (!batched || g.sA % 4 == 0);
-  p.vec_b = aligned16(g.B) && g.ldb % 4 == 0 && b_contig % 4 == 0 && (!batched || g.sB % 4 == 0);
-  p.vec_c = aligned16(g.C) && g.ldc % 4 == 0 && (!batched || g.sC % 4 == 0);
-  const size_t gx = (g.m + BM - 1) / BM, gy = (g.n + BN - 1) / BN;
-  if (gy > 65535 || g.batch > 65535) return MMBO_ERR_TOO_LARGE;
-  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch), block((BM / TTM) * (BN / TTN));
-  const float* A = static_cast<const float*>(g.A);
-  const float* B = static_cast<const float*>(g.B);
-  float* C = static_cast<float*>(g.C);
-  if (!g.transA && !g.transB)
-    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, false, false><<<grid, block, 0, st>>>(A, B, C, p);
-  else if (!g.transA && g.transB)
-    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, false, true><<<grid, block, 0, st>>>(A, B, C, p);
-  else if (g.transA && !g.transB)
-    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, true, false><<<grid, block, 0, st>>>(A, B, C, p);
-  else
-    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, true, true><<<grid, block, 0, st>>>(A, B, C, p);
-  MMBO_COUNT_LAUNCH();
-  return (int)cudaGetLastError();
-}
-
-// The tcgen05 kernel addresses its operands through TMA: 16-byte aligned bases and
-// leading dimensions that are multiples of 8 fp16 elements.
-static bool hgemm_tma_ok(const GemmArgs& g) {
-  return aligned16(g.A) && aligned16(g.B) && g.lda % 8 == 0 && g.ldb % 8 == 0 && g.k > 0;
-}
-
-template <int TM, int STAGES, int CG, int EW, bool AK, bool BK_>
-static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                             const HgemmParams& p, const HgemmPeerMaps& peers, uint64_t tiles, cudaStream_t st) {
-  using L = HgemmSmem<TM, STAGES, CG, EW>;
-  auto kern = hgemm_tcgen05_kernel<TM, STAGES, AK, BK_, CG, EW>;
-  static bool attr_done[kMaxDevices] = {};
-  static int max_walkers[kMaxDevices] = {};
-  const int dev = current_device();
-  if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
-  if (!attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
-    if (e != cudaSuccess) return (int)e;
-    int walkers = sm_count() / CG;
-    if (CG == 2) {
-      // How many CTA pairs the device can hold at once (GPCs with an odd number of
-      // SMs leave one SM unpaired).
-      cudaLaunchConfig_t q = {};
-      q.gridDim = dim3((unsigned)(2 * walkers));
-      q.blockDim = dim3(L::kThreads);
-      q.dynamicSmemBytes = L::kDynamic;
-      cudaLaunchAttribute qa[1];
-      qa[0].id = cudaLaunchAttributeClusterDimension;
-      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
-      q.attrs = qa; q.numAttrs = 1;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, kern, &q) == cudaSuccess && n > 0) walkers = n < walkers ? n : walkers;
-      else cudaGetLastError();
-    }
-    max_walkers[dev] = walkers;
-    attr_done[dev] = true;
-  }
-  const unsigned walkers = (unsigned)(tiles < (uint64_t)max_walkers[dev] ? tiles : (uint64_t)max_walkers[dev]);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(walkers * CG);
-  cfg.blockDim = dim3(L::kThreads);
-  cfg.dynamicSmemBytes = L::kDynamic;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
-  MMBO_COUNT_LAUNCH();
-  return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p, peers);
-}
-
-template <int TM, int STAGES, int CG, int EW = 4>
-static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
-  CUtensorMap ta, tb, tc;
-  int rc;
-  constexpr auto F16 = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  constexpr auto SW = CU_TENSOR_MAP_SWIZZLE_128B;
-  // op(A): K-major when transposed (stored k x m), MN-major otherwise (stored m x k).
-  if (g.transA)
-    rc = make_map(&ta, F16, 2, g.A, g.k, g.m, g.lda, kBlockK, TM / CG, SW, g.batch, g.sA);
-  else
-    rc = make_map(&ta, F16, 2, g.A, g.m, g.k, g.lda, 64, kBlockK, SW, g.batch, g.sA);
-  if (rc) return rc;
-  // op(B): K-major when not transposed (stored k x n), MN-major otherwise (stored n x k).
-  if (!g.transB)
-    rc = make_map(&tb, F16, 2, g.B, g.k, g.n, g.ldb, kBlockK, kTileN, SW, g.batch, g.sB);
-  else
-    rc = make_map(&tb, F16, 2, g.B, g.n, g.k, g.ldb, 64, kBlockK, SW, g.batch, g.sB);
-  if (rc) return rc;
-  // C through TMA only when whole 16-byte units stay inside the matrix (see HgemmParams).
-  const bool c_tma = aligned16(g.C) && g.ldc % 8 == 0 && g.m % 8 == 0 && batch_stride_ok(g.batch, g.sC, 2);
-  if (c_tma) {
-    rc = make_map(&tc, F16, 2, g.C, g.m, g.n, g.ldc, 64, 32, SW, g.batch, g.sC);
-    if (rc) return rc;
-  } else {
-    tc = ta;  // placeholder, never dereferenced by the plain epilogue
-  }
-  static HgemmPeerMaps peers;  // (callers hold the library lock)
-  peers.count = 0;
-  if (g.npeers > 0) {
-    // peer copies go through TMA stores only, and only for a single problem
-    if (!c_tma || g.npeers > kMaxPeerCopies || g.batch != 1) return MMBO_ERR_KERNEL_UNSUITABLE;
-    for (int d = 0; d < g.npeers; ++d) {
-      if (!g.peers[d] || !aligned16(g.peers[d])) return MMBO_ERR_KERNEL_UNSUITABLE;
-      rc = make_map_2d(&peers.map[d], F16, 2, g.peers[d], g.m, g.n, g.ldc, 64, 32);
-      if (rc) return rc;
-    }
-    peers.count = (uint32_t)g.npeers;
-  }
-
-  HgemmParams p;
-  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
-  p.tiles_m = (uint32_t)((g.m + TM - 1) / TM);
-  p.tiles_n = (uint32_t)((g.n + kTileN * CG - 1) / (kTileN * CG));
-  p.batch = (uint32_t)g.batch;
-  p.c_batch_stride = g.sC;
-  p.wgm = wgm;
-  p.alpha = g.alpha; p.beta = g.beta;
-  p.c = static_cast<__half*>(g.C); p.ldc = (uint32_t)g.ldc; p.c_tma = c_tma ? 1u : 0u;
-  p.c_mc = nullptr;
-  if (g.c_multicast) {
-    // the multicast window is written with 16-byte stores of whole column pieces
-    if (!c_tma || g.batch != 1 || !aligned16(g.c_multicast) || g.npeers > 0) return MMBO_ERR_KERNEL_UNSUITABLE;
-    p.c_mc = static_cast<__half*>(g.c_multicast);
-  }
-  p.trace = g_trace_buffer;  // null unless mmbo_debug_trace armed it
-  p.diag = settings().diag;  // diagnostic builds (no C store / no drain): never set in production
-  const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n * g.batch;
-  if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-  if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, true>(ta, tb, tc, p, peers, tiles, st);
-  if (g.transA && g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, false>(ta, tb, tc, p, peers, tiles, st);
-  if (!g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, false, true>(ta, tb, tc, p, peers, tiles, st);
-  return launch_hgemm_inst<TM, STAGES, CG, EW, false, false>(ta, tb, tc, p, peers, tiles, st);
-}
-
 // ------------------------------------------------------------------ scratch memory --
 // One scratch buffer per device, used by the kernels that repack operands (the 3xTF32
 // SGEMM, fp16 operands TMA cannot address, split-K partial sums).  Either the caller lends
@@ -559,6 +341,298 @@ static int workspace_release(cudaStream_t st) {
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Stream-K (stream_k.cuh) for the persistent producer / consumer kernels: decided per call.  `slots` = CTAs
+// resident at once; a unit is one k-slab of one tile.  Splitting pays when whole-tile rounds leave the last
+// round part empty; each CTA then writes or reads at most one tile of partial sums (about `overhead_units`
+// slabs' worth of time).  split_k = 1 switches it off, > 1 forces it wherever the problem has enough slabs.
+struct SkPlan {
+  bool on;
+  unsigned grid;
+  size_t flag_bytes, total_bytes;
+};
+// Split mode the tuning table holds for the problem of the call in progress (0: none); set by the table
+// lookup of automatic selection, consulted when the option itself says "automatic".
+static uint32_t g_split_from_table = 0;
+
+static SkPlan plan_stream_k(size_t tiles, size_t num_kb, size_t slots, size_t partial_bytes, int warps, size_t batch) {
+  SkPlan pl{false, 0, 0, 0};
+  const uint32_t mode = settings().split_k ? settings().split_k : g_split_from_table;
+  const unsigned long long units = (unsigned long long)tiles * num_kb;
+  if (mode == 1 || batch != 1 || tiles == 0 || num_kb < 8 || units >= (1ull << 40)) return pl;
+  size_t grid = slots;
+  if (units / 8 < grid) grid = (size_t)(units / 8);  // at least 8 slabs per CTA
+  if (grid < 2) return pl;
+  if (mode == 0) {
+    const double overhead_units = 6.0;
+    const double dp = (double)((tiles + slots - 1) / slots) * (double)num_kb;
+    const double sk = (double)units / (double)grid + overhead_units;
+    if (!(dp > 1.04 * sk)) return pl;
+  }
+  pl.on = true;
+  pl.grid = (unsigned)grid;
+  pl.flag_bytes = align_up(grid * (size_t)warps * 4, 1024);
+  pl.total_bytes = pl.flag_bytes + grid * partial_bytes;
+  return pl;
+}
+// Scratch of a stream-K launch: cleared flags first, one tile of partial sums per CTA behind them.
+static int prepare_stream_k(const SkPlan& pl, cudaStream_t st, StreamK* sk) {
+  sk->enabled = 0; sk->epoch = 1; sk->flags = nullptr; sk->partials = nullptr;
+  if (!pl.on) return MMBO_OK;
+  void* scratch = nullptr;
+  int rc = ensure_workspace(pl.total_bytes, &scratch);
+  if (rc) return rc;
+  if ((rc = workspace_acquire(st))) return rc;
+  cudaError_t e = cudaMemsetAsync(scratch, 0, pl.flag_bytes, st);
+  if (e != cudaSuccess) return (int)e;
+  sk->enabled = 1;
+  sk->flags = static_cast<unsigned int*>(scratch);
+  sk->partials = static_cast<char*>(scratch) + pl.flag_bytes;
+  return MMBO_OK;
+}
+
+// ------------------------------------------------------------------ launches ---------
+template <typename T>
+static int launch_simple(const GemmArgs& g, cudaStream_t st) {
+  const size_t gx = (g.m + 31) / 32, gy = (g.n + 7) / 8;
+  if (gy > 65535 || gx > 0x7fffffffull || g.batch > 65535) return MMBO_ERR_TOO_LARGE;
+  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch), block(32, 8);
+  gemm_simple_kernel<T><<<grid, block, 0, st>>>(g.transA, g.transB, g.m, g.n, g.k, g.alpha,
+                                                static_cast<const T*>(g.A), g.lda,
+                                                static_cast<const T*>(g.B), g.ldb, g.beta,
+                                                static_cast<T*>(g.C), g.ldc, g.sA, g.sB, g.sC);
+  MMBO_COUNT_LAUNCH();
+  return (int)cudaGetLastError();
+}
+
+template <typename T>
+static int launch_scale(const GemmArgs& g, cudaStream_t st) {
+  const size_t gx = (g.m + 31) / 32, gy = (g.n + 7) / 8;
+  if (gy > 65535 || gx > 0x7fffffffull || g.batch > 65535) return MMBO_ERR_TOO_LARGE;
+  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch), block(32, 8);
+  scale_c_kernel<T><<<grid, block, 0, st>>>(g.m, g.n, g.beta, static_cast<T*>(g.C), g.ldc, g.sC);
+  MMBO_COUNT_LAUNCH();
+  return (int)cudaGetLastError();
+}
+
+// FFMA kernel with a producer warpgroup: an operand goes through TMA when its tile rows are
+// contiguous in memory, its base 16-byte aligned and its leading dimension a multiple of 4.
+static int launch_sgemm_ffma_ws(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
+  SgemmParams p;
+  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
+  p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
+  p.alpha = g.alpha; p.beta = g.beta; p.wgm = wgm;
+  p.batch_a = p.batch_b = p.batch_c = 0;
+  p.vec_a = p.vec_b = 0;
+  p.vec_c = aligned16(g.C) && g.ldc % 4 == 0;
+  SgemmWsFlags f;
+  f.tma_a = !g.transA && aligned16(g.A) && g.lda % 4 == 0;
+  f.tma_b = g.transB && aligned16(g.B) && g.ldb % 4 == 0;
+  CUtensorMap ta, tb;
+  memset(&ta, 0, sizeof(ta));
+  memset(&tb, 0, sizeof(tb));
+  if (f.tma_a) {
+    const int rc = make_map_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.A, g.m, g.k, g.lda, kFwBM + kFwPad, kFwBK,
+                               CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+  }
+  if (f.tma_b) {
+    const int rc = make_map_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.B, g.n, g.k, g.ldb, kFwBN + kFwPad, kFwBK,
+                               CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+  }
+  const size_t tiles = ((g.m + kFwBM - 1) / kFwBM) * ((g.n + kFwBN - 1) / kFwBN);
+  if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
+  // Eight CTAs per SM in the grid, two resident: as CTAs finish their few tiles the hardware starts the
+  // next ones, which balances the end of the launch (4096^3: 61.1 TFLOP/s against 52.3 with 2 per SM).
+  unsigned grid = (unsigned)std::min(tiles, (size_t)8 * (size_t)sm_count());
+  // Few tiles: stream-K over the two resident CTAs per SM instead (all of them run at once, which the
+  // flag hand-over between CTAs relies on).
+  SkPlan plan{false, 0, 0, 0};
+  if (tiles < (size_t)8 * (size_t)sm_count())
+    plan = plan_stream_k(tiles, (g.k + kFwBK - 1) / kFwBK, (size_t)2 * (size_t)sm_count(), (size_t)kFwBM * kFwBN * 4,
+                         kFwConsumerWarps, g.batch);
+  StreamK sk;
+  {
+    const int rc = prepare_stream_k(plan, st, &sk);
+    // scratch that cannot be had (a lent buffer that is too small) is no error: whole tiles then
+    if (rc == MMBO_OK && plan.on) grid = plan.grid;
+    else sk.enabled = 0;
+  }
+  const float* A = static_cast<const float*>(g.A);
+  const float* B = static_cast<const float*>(g.B);
+  float* C = static_cast<float*>(g.C);
+  auto launch = [&](auto kernel) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    kernel<<<grid, kFwThreads, kFwSmemBytes, st>>>(ta, tb, A, B, C, p, f, sk);
+    MMBO_COUNT_LAUNCH();
+    int rc = (int)cudaGetLastError();
+    if (sk.enabled) {
+      const int rc2 = workspace_release(st);
+      if (!rc) rc = rc2;
+    }
+    return rc;
+  };
+  if (sk.enabled) {
+    if (!g.transA && !g.transB) return launch(sgemm_ffma_ws_kernel<false, false, true>);
+    if (!g.transA && g.transB) return launch(sgemm_ffma_ws_kernel<false, true, true>);
+    if (g.transA && !g.transB) return launch(sgemm_ffma_ws_kernel<true, false, true>);
+    return launch(sgemm_ffma_ws_kernel<true, true, true>);
+  }
+  if (!g.transA && !g.transB) return launch(sgemm_ffma_ws_kernel<false, false>);
+  if (!g.transA && g.transB) return launch(sgemm_ffma_ws_kernel<false, true>);
+  if (g.transA && !g.transB) return launch(sgemm_ffma_ws_kernel<true, false>);
+  return launch(sgemm_ffma_ws_kernel<true, true>);
+}
+
+template <int BM, int BN, int TTM, int TTN>
+static int launch_sgemm_ffma(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
+  constexpr int BK = 16;
+  SgemmParams p;
+  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
+  p.lda = (uint32_t)g.lda; p.ldb = (uint32_t)g.ldb; p.ldc = (uint32_t)g.ldc;
+  p.alpha = g.alpha; p.beta = g.beta; p.wgm = wgm;
+  p.batch_a = g.sA; p.batch_b = g.sB; p.batch_c = g.sC;
+  // 128-bit accesses: base and pitch 16-byte aligned, and the contiguous extent a
+  // multiple of 4 so that no vector straddles the matrix edge (every problem of a batch).
+  const bool batched = g.batch > 1;
+  const size_t a_contig = g.transA ? g.k : g.m, b_contig = g.transB ? g.n : g.k;
+  p.vec_a = aligned16(g.A) && g.lda % 4 == 0 && a_contig % 4 == 0 && (!batched || g.sA % 4 == 0);
+  p.vec_b = aligned16(g.B) && g.ldb % 4 == 0 && b_contig % 4 == 0 && (!batched || g.sB % 4 == 0);
+  p.vec_c = aligned16(g.C) && g.ldc % 4 == 0 && (!batched || g.sC % 4 == 0);
+  const size_t gx = (g.m + BM - 1) / BM, gy = (g.n + BN - 1) / BN;
+  if (gy > 65535 || g.batch > 65535) return MMBO_ERR_TOO_LARGE;
+  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch), block((BM / TTM) * (BN / TTN));
+  const float* A = static_cast<const float*>(g.A);
+  const float* B = static_cast<const float*>(g.B);
+  float* C = static_cast<float*>(g.C);
+  if (!g.transA && !g.transB)
+    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, false, false><<<grid, block, 0, st>>>(A, B, C, p);
+  else if (!g.transA && g.transB)
+    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, false, true><<<grid, block, 0, st>>>(A, B, C, p);
+  else if (g.transA && !g.transB)
+    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, true, false><<<grid, block, 0, st>>>(A, B, C, p);
+  else
+    sgemm_ffma_kernel<BM, BN, BK, TTM, TTN, true, true><<<grid, block, 0, st>>>(A, B, C, p);
+  MMBO_COUNT_LAUNCH();
+  return (int)cudaGetLastError();
+}
+
+// The tcgen05 kernel addresses its operands through TMA: 16-byte aligned bases and
+// leading dimensions that are multiples of 8 fp16 elements.
+static bool hgemm_tma_ok(const GemmArgs& g) {
+  return aligned16(g.A) && aligned16(g.B) && g.lda % 8 == 0 && g.ldb % 8 == 0 && g.k > 0;
+}
+
+template <int TM, int STAGES, int CG, int EW, bool AK, bool BK_, int CSETS = (EW == 8 ? 2 : 1)>
+static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                             const HgemmParams& p, const HgemmPeerMaps& peers, uint64_t tiles, cudaStream_t st) {
+  using L = HgemmSmem<TM, STAGES, CG, EW, CSETS>;
+  auto kern = hgemm_tcgen05_kernel<TM, STAGES, AK, BK_, CG, EW, CSETS>;
+  static bool attr_done[kMaxDevices] = {};
+  static int max_walkers[kMaxDevices] = {};
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return MMBO_ERR_TOO_LARGE;
+  if (!attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess) return (int)e;
+    int walkers = sm_count() / CG;
+    if (CG == 2) {
+      // How many CTA pairs the device can hold at once (GPCs with an odd number of
+      // SMs leave one SM unpaired).
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3((unsigned)(2 * walkers));
+      q.blockDim = dim3(L::kThreads);
+      q.dynamicSmemBytes = L::kDynamic;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa; q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &q) == cudaSuccess && n > 0) walkers = n < walkers ? n : walkers;
+      else cudaGetLastError();
+    }
+    max_walkers[dev] = walkers;
+    attr_done[dev] = true;
+  }
+  const unsigned walkers = (unsigned)(tiles < (uint64_t)max_walkers[dev] ? tiles : (uint64_t)max_walkers[dev]);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(walkers * CG);
+  cfg.blockDim = dim3(L::kThreads);
+  cfg.dynamicSmemBytes = L::kDynamic;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  MMBO_COUNT_LAUNCH();
+  return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p, peers);
+}
+
+template <int TM, int STAGES, int CG, int EW = 4, int CSETS = (EW == 8 ? 2 : 1)>
+static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st) {
+  CUtensorMap ta, tb, tc;
+  int rc;
+  constexpr auto F16 = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  constexpr auto SW = CU_TENSOR_MAP_SWIZZLE_128B;
+  // op(A): K-major when transposed (stored k x m), MN-major otherwise (stored m x k).
+  if (g.transA)
+    rc = make_map(&ta, F16, 2, g.A, g.k, g.m, g.lda, kBlockK, TM / CG, SW, g.batch, g.sA);
+  else
+    rc = make_map(&ta, F16, 2, g.A, g.m, g.k, g.lda, 64, kBlockK, SW, g.batch, g.sA);
+  if (rc) return rc;
+  // op(B): K-major when not transposed (stored k x n), MN-major otherwise (stored n x k).
+  if (!g.transB)
+    rc = make_map(&tb, F16, 2, g.B, g.k, g.n, g.ldb, kBlockK, kTileN, SW, g.batch, g.sB);
+  else
+    rc = make_map(&tb, F16, 2, g.B, g.n, g.k, g.ldb, 64, kBlockK, SW, g.batch, g.sB);
+  if (rc) return rc;
+  // C through TMA only when whole 16-byte units stay inside the matrix (see HgemmParams).
+  const bool c_tma = aligned16(g.C) && g.ldc % 8 == 0 && g.m % 8 == 0 && batch_stride_ok(g.batch, g.sC, 2);
+  if (c_tma) {
+    rc = make_map(&tc, F16, 2, g.C, g.m, g.n, g.ldc, 64, 32, SW, g.batch, g.sC);
+    if (rc) return rc;
+  } else {
+    tc = ta;  // placeholder, never dereferenced by the plain epilogue
+  }
+  static HgemmPeerMaps peers;  // (callers hold the library lock)
+  peers.count = 0;
+  if (g.npeers > 0) {
+    // peer copies go through TMA stores only, and only for a single problem
+    if (!c_tma || g.npeers > kMaxPeerCopies || g.batch != 1) return MMBO_ERR_KERNEL_UNSUITABLE;
+    for (int d = 0; d < g.npeers; ++d) {
+      if (!g.peers[d] || !aligned16(g.peers[d])) return MMBO_ERR_KERNEL_UNSUITABLE;
+      rc = make_map_2d(&peers.map[d], F16, 2, g.peers[d], g.m, g.n, g.ldc, 64, 32);
+      if (rc) return rc;
+    }
+    peers.count = (uint32_t)g.npeers;
+  }
+
+  HgemmParams p;
+  p.m = (uint32_t)g.m; p.n = (uint32_t)g.n; p.k = (uint32_t)g.k;
+  p.tiles_m = (uint32_t)((g.m + TM - 1) / TM);
+  p.tiles_n = (uint32_t)((g.n + kTileN * CG - 1) / (kTileN * CG));
+  p.batch = (uint32_t)g.batch;
+  p.c_batch_stride = g.sC;
+  p.wgm = wgm;
+  p.alpha = g.alpha; p.beta = g.beta;
+  p.c = static_cast<__half*>(g.C); p.ldc = (uint32_t)g.ldc; p.c_tma = c_tma ? 1u : 0u;
+  p.c_mc = nullptr;
+  if (g.c_multicast) {
+    // the multicast window is written with 16-byte stores of whole column pieces
+    if (!c_tma || g.batch != 1 || !aligned16(g.c_multicast) || g.npeers > 0) return MMBO_ERR_KERNEL_UNSUITABLE;
+    p.c_mc = static_cast<__half*>(g.c_multicast);
+  }
+  p.trace = g_trace_buffer;  // null unless mmbo_debug_trace armed it
+  p.diag = settings().diag;  // diagnostic builds (no C store / no drain): never set in production
+  const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n * g.batch;
+  if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
+  if (g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, true, CSETS>(ta, tb, tc, p, peers, tiles, st);
+  if (g.transA && g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, true, false, CSETS>(ta, tb, tc, p, peers, tiles, st);
+  if (!g.transA && !g.transB) return launch_hgemm_inst<TM, STAGES, CG, EW, false, true, CSETS>(ta, tb, tc, p, peers, tiles, st);
+  return launch_hgemm_inst<TM, STAGES, CG, EW, false, false, CSETS>(ta, tb, tc, p, peers, tiles, st);
+}
 
 // Scratch layout of the 3xTF32 SGEMM: A_hi, A_lo (batch x m rows of Kpad floats), B_hi, B_lo (batch x n rows).
 struct Tf32Scratch {
@@ -680,30 +754,36 @@ static int run_tf32x3(const GemmArgs& g, void* scratch, uint32_t wgm, cudaStream
 // mmbo_tuning_set, from a file given to mmbo_tuning_load, or from the file named by the
 // environment variable MMBO_TUNING_FILE (read once, on the first automatic selection).
 // File format, one row per line, '#' starts a comment:
-//     <dtype f16|f32|f64> <trans NN|NT|TN|TT> <m> <n> <k> <kernelId>
+//     <dtype f16|f32|f64> <trans NN|NT|TN|TT> <m> <n> <k> <kernelId> [<split>]
+// split (optional, default 0): how the contraction is split for this problem -- 0 decided per call, 1 never,
+// 2 always (stream-K, rows that have it) -- the counterpart of a tuned GlobalSplitU value
+// (src/gemm/ref/vega20_Cijk_Ailk_Bjlk_DB.yaml:69-71).
 struct TuneRow {
   int dtype, ta, tb;
   size_t m, n, k;
   int kernel;
+  int split;
 };
 constexpr int kMaxTuneRows = 4096;
 static TuneRow g_tune[kMaxTuneRows];
 static int g_tune_count = 0;
 static bool g_tune_env_done = false;
 
-static int tune_set(int dtype, int ta, int tb, size_t m, size_t n, size_t k, int kernel) {
+static int tune_set(int dtype, int ta, int tb, size_t m, size_t n, size_t k, int kernel, int split = 0) {
   int count = 0;
   if (!rows_of(dtype, &count)) return MMBO_ERR_BAD_DTYPE;
   if (kernel < 0 || kernel >= count) return MMBO_ERR_BAD_KERNEL_ID;
+  if (split < 0 || split > 2) return MMBO_ERR_BAD_OPTION;
   for (int i = 0; i < g_tune_count; ++i) {
     TuneRow& r = g_tune[i];
     if (r.dtype == dtype && r.ta == ta && r.tb == tb && r.m == m && r.n == n && r.k == k) {
       r.kernel = kernel;
+      r.split = split;
       return MMBO_OK;
     }
   }
   if (g_tune_count >= kMaxTuneRows) return MMBO_ERR_TOO_LARGE;
-  g_tune[g_tune_count++] = TuneRow{dtype, ta, tb, m, n, k, kernel};
+  g_tune[g_tune_count++] = TuneRow{dtype, ta, tb, m, n, k, kernel, split};
   return MMBO_OK;
 }
 
@@ -715,14 +795,14 @@ static int tune_load(const char* path) {
   while (fgets(line, sizeof line, f)) {
     char dt[8], tr[8];
     unsigned long long m, n, k;
-    int kernel;
+    int kernel, split = 0;
     if (line[0] == '#' || line[0] == '\n') continue;
-    if (sscanf(line, "%7s %7s %llu %llu %llu %d", dt, tr, &m, &n, &k, &kernel) != 6) { rc = MMBO_ERR_TUNING_FILE; break; }
+    if (sscanf(line, "%7s %7s %llu %llu %llu %d %d", dt, tr, &m, &n, &k, &kernel, &split) < 6) { rc = MMBO_ERR_TUNING_FILE; break; }
     const int dtype = !strcmp(dt, "f16") ? MMBO_DTYPE_F16 : !strcmp(dt, "f32") ? MMBO_DTYPE_F32
                       : !strcmp(dt, "f64") ? MMBO_DTYPE_F64 : -1;
     if (dtype < 0 || strlen(tr) != 2) { rc = MMBO_ERR_TUNING_FILE; break; }
-    rc = tune_set(dtype, tr[0] == 'T', tr[1] == 'T', m, n, k, kernel);
-    if (rc) break;
+    rc = tune_set(dtype, tr[0] == 'T', tr[1] == 'T', m, n, k, kernel, split);
+    if (rc) { rc = MMBO_ERR_TUNING_FILE; break; }
   }
   fclose(f);
   return rc;
@@ -737,8 +817,10 @@ static int tune_lookup(int dtype, const GemmArgs& g) {
   }
   for (int i = 0; i < g_tune_count; ++i) {
     const TuneRow& r = g_tune[i];
-    if (r.dtype == dtype && r.ta == g.transA && r.tb == g.transB && r.m == g.m && r.n == g.n && r.k == g.k)
+    if (r.dtype == dtype && r.ta == g.transA && r.tb == g.transB && r.m == g.m && r.n == g.n && r.k == g.k) {
+      g_split_from_table = (uint32_t)r.split;
       return r.kernel;
+    }
   }
   return -1;
 }
@@ -795,9 +877,12 @@ static int select_f16(const GemmArgs& g) {
   const double s1 = 0.80 * eff(t1, sms) * fill(t1, 256, 128);
   const double s2 = 0.70 * eff(t2, sms) * fill(t2, 128, 128);
   const double s3 = 1.00 * eff(t3, sms / 2) * fill(t3, 256, 256);
-  // Short contractions are bound by how fast accumulators are drained: the variant with
-  // eight epilogue warps wins there and ties on long ones.
-  if (s3 >= s1 && s3 >= s2) return g.k <= 1024 ? 4 : 3;
+  // Short contractions are bound by the epilogue: the rows with eight epilogue warps win there.  Up to
+  // k = 512 the one that requests the old C a whole tile ahead into a second set of staging buffers
+  // (three operand stages); up to k = 2048 the one with five stages and an L2 prefetch of the next tile's
+  // C instead (8192 x 8192 x 1024, beta = 1: 131 against 137 us; x 2048: 229 against 248 us; x 512: 92
+  // against 89 us); the six-stage row with four epilogue warps beyond.
+  if (s3 >= s1 && s3 >= s2) return g.k <= 512 ? 4 : g.k <= 2048 ? 5 : 3;
   return s1 >= s2 ? 1 : 2;
 }
 
@@ -846,12 +931,19 @@ static int select_f64(const GemmArgs& g) {
   const size_t slots = 2 * (size_t)sm_count();  // CTAs resident at once
   const size_t tiles128 = g.batch * ((g.m + 127) / 128) * ((g.n + kWsBN - 1) / kWsBN);
   const size_t tiles64 = g.batch * ((g.m + 63) / 64) * ((g.n + kWsBN - 1) / kWsBN);
-  if (g.k <= 512 || tiles128 < slots) return 4;
-  // Longer contractions: the tile height whose tile count fills whole rounds of CTA slots better
-  // (2368^3 with 128-row tiles: 703 tiles = 2.4 rounds, 27.4 TFLOP/s against 34.4 at 2176^3 = 1.95
-  // rounds); the 64-row tiles are about 1.5 % slower per tile.
-  auto fill = [&](size_t tiles) { return (double)tiles / (double)(((tiles + slots - 1) / slots) * slots); };
-  return 0.985 * fill(tiles64) > fill(tiles128) ? 4 : 3;
+  if (g.k <= 512) return 4;
+  // Longer contractions: estimated time of each tile height in slabs of a 64-row tile -- whole rounds of the
+  // CTA slots, or the even split of stream-K where that applies (plan_stream_k) -- the 64-row tiles being
+  // about 1.5 % slower per unit of work (3072^3: 34.8 / 34.3 TFLOP/s).  Without stream-K the tile height whose
+  // tile count fills whole rounds better wins (2368^3 with 128-row tiles: 703 tiles = 2.4 rounds, 27.4 TFLOP/s
+  // against 34.4 at 2176^3 = 1.95 rounds).
+  const size_t num_kb = (g.k + kWsBK - 1) / kWsBK;
+  auto slabs = [&](size_t tiles, size_t bm) {
+    const SkPlan pl = plan_stream_k(tiles, num_kb, slots, bm * kWsBN * 8, kWsConsumers, g.batch);
+    if (pl.on) return (double)tiles * (double)num_kb / (double)pl.grid + 6.0;
+    return (double)((tiles + slots - 1) / slots) * (double)num_kb;
+  };
+  return 1.015 * slabs(tiles64, 64) < 2.0 * slabs(tiles128, 128) ? 4 : 3;
 }
 
 static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStream_t st) {
@@ -894,7 +986,15 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
     const size_t bm = id == 3 ? 128 : 64;
     const size_t tiles = ((g.m + bm - 1) / bm) * ((g.n + kWsBN - 1) / kWsBN) * g.batch;
     if (tiles > 0x7fffffffull) return MMBO_ERR_TOO_LARGE;
-    const unsigned grid3 = (unsigned)std::min(tiles, (size_t)2 * (size_t)sm_count());  // two CTAs per SM (more made no difference)
+    unsigned grid3 = (unsigned)std::min(tiles, (size_t)2 * (size_t)sm_count());  // two CTAs per SM (more made no difference)
+    const SkPlan plan = plan_stream_k(tiles, (g.k + kWsBK - 1) / kWsBK, (size_t)2 * (size_t)sm_count(), bm * kWsBN * 8,
+                                      kWsConsumers, g.batch);
+    StreamK sk;
+    {
+      const int rc = prepare_stream_k(plan, st, &sk);
+      if (rc == MMBO_OK && plan.on) grid3 = plan.grid;
+      else sk.enabled = 0;  // no scratch to be had (a lent buffer that is too small): whole tiles
+    }
     // An operand goes through TMA when its base is 16-byte aligned and its leading dimension even
     // (strides in multiples of 16 bytes); the box is kWsPad elements wider than the tile along the
     // contiguous index, which gives the slab its padded pitch.
@@ -932,12 +1032,21 @@ static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStr
     auto launch = [&](auto kernel, size_t smem) -> int {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
-      kernel<<<grid3, kWsThreads, smem, st>>>(ta, tb, tc, A, B, C, p);
+      kernel<<<grid3, kWsThreads, smem, st>>>(ta, tb, tc, A, B, C, p, sk);
       MMBO_COUNT_LAUNCH();
-      return (int)cudaGetLastError();
+      int rc = (int)cudaGetLastError();
+      if (sk.enabled) {
+        const int rc2 = workspace_release(st);
+        if (!rc) rc = rc2;
+      }
+      return rc;
     };
     auto by_tile = [&](auto ta_, auto tb_) -> int {
       constexpr bool TA = decltype(ta_)::value, TB = decltype(tb_)::value;
+      if (sk.enabled) {
+        if (id == 3) return launch(dgemm_dmma_ws_kernel<TA, TB, 128, true>, WsTile<128, TA, !TB>::kSmemBytes);
+        return launch(dgemm_dmma_ws_kernel<TA, TB, 64, true>, WsTile<64, TA, !TB>::kSmemBytes);
+      }
       if (id == 3) return launch(dgemm_dmma_ws_kernel<TA, TB, 128>, WsTile<128, TA, !TB>::kSmemBytes);
       return launch(dgemm_dmma_ws_kernel<TA, TB, 64>, WsTile<64, TA, !TB>::kSmemBytes);
     };
@@ -1008,6 +1117,7 @@ static int run_f16(const GemmArgs& g_in, int id, cudaStream_t st) {
     case 2: rc = launch_hgemm_tcgen05<128, 6, 1>(g, wgm_of(kF16Rows[2]), st); break;
     case 3: rc = launch_hgemm_tcgen05<256, 6, 2>(g, wgm_of(kF16Rows[3]), st); break;
     case 4: rc = launch_hgemm_tcgen05<256, 3, 2, 8>(g, wgm_of(kF16Rows[4]), st); break;
+    case 5: rc = launch_hgemm_tcgen05<256, 5, 2, 8, 1>(g, wgm_of(kF16Rows[5]), st); break;
     default: rc = MMBO_ERR_BAD_KERNEL_ID;
   }
   if (scratch_used) {
@@ -1334,8 +1444,9 @@ int mmbo_gemm_f16_sharded_host(int nGpus, int rank, void* ncclComm, int transA, 
   size_t col0 = 0, ncols = 0;
   int rc = shard_check(nGpus, rank, ncclComm, true, n, &col0, &ncols);
   if (rc) return rc;
+  // Every rank takes part in the exchange of A, so every rank must own columns: the same answer on all ranks.
+  if (m != 0 && n != 0 && (n + 255) / 256 < (size_t)nGpus) return MMBO_ERR_BAD_SHARD;
   GemmArgs g{transA, transB, m, ncols, k, A, B_block, C_block, lda, ldb, ldc, 0.f, 0.f};
-  if (ncols == 0) g.C = g.C ? g.C : const_cast<void*>(A);  // an empty block still takes part in the exchange of A
   if ((rc = validate(g, alpha, beta))) return rc;
   g.alpha = *alpha;
   g.beta = *beta;
@@ -1665,6 +1776,12 @@ int mmbo_tuning_set(int dtype, int transA, int transB, size_t m, size_t n, size_
   MMBO_API_LOCK();
   if ((transA != 0 && transA != 1) || (transB != 0 && transB != 1)) return MMBO_ERR_BAD_TRANS;
   return tune_set(dtype, transA, transB, m, n, k, kernelId);
+}
+
+int mmbo_tuning_set_split(int dtype, int transA, int transB, size_t m, size_t n, size_t k, int kernelId, int split) {
+  MMBO_API_LOCK();
+  if ((transA != 0 && transA != 1) || (transB != 0 && transB != 1)) return MMBO_ERR_BAD_TRANS;
+  return tune_set(dtype, transA, transB, m, n, k, kernelId, split);
 }
 
 int mmbo_tuning_load(const char* path) {

@@ -114,11 +114,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 #pragma unroll 1
   for (uint32_t i = 0; i < 1024u; ++i)
     if (mbar_try_wait(bar, parity)) return true;
+  // A wait that has lasted this long is a long one (a whole main loop, a busy copy engine): back off
+  // between polls so that the waiting thread stops competing for issue slots and power.
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 255u) == 0u) {
+    __nanosleep(128);
+    if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
       if (global_timer_ns() - t0 > limit_ns) {
         report_fault(fault_code, detail);
@@ -127,6 +130,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       }
     }
   }
+}
+
+// The same for a whole (converged) warp: lane 0 polls, the other lanes rest at the shuffle; once the
+// phase has completed every lane observes it itself (one poll that succeeds at once), which gives each
+// lane the ordering a wait of its own would have given.  The result is warp-uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               unsigned int fault_code, unsigned int detail) {
+  uint32_t ok = 1u;
+  if ((threadIdx.x & 31u) == 0u) ok = mbar_wait(bar, parity, abort_flag, fault_code, detail) ? 1u : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok) {
+#pragma unroll 1
+    for (uint32_t i = 0; i < 64u && !mbar_try_wait(bar, parity); ++i) {
+    }
+  }
+  return ok != 0u;
 }
 
 // ---------------------------------------------------------------- packed fp32 ---------

@@ -25,6 +25,7 @@
 #include "ptx.cuh"
 #include "raster.h"
 #include "sgemm_ffma.cuh"  // SgemmParams
+#include "stream_k.cuh"
 
 namespace mmbo {
 
@@ -75,11 +76,11 @@ __device__ __forceinline__ void fw_fill_elements(uint32_t slab, const float* __r
   }
 }
 
-template <bool TRANS_A, bool TRANS_B>
+template <bool TRANS_A, bool TRANS_B, bool SK = false>
 __global__ void __launch_bounds__(kFwThreads, 2)
 sgemm_ffma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
-                     const SgemmParams p, const SgemmWsFlags f) {
+                     const SgemmParams p, const SgemmWsFlags f, const StreamK sk) {
   extern __shared__ __align__(16) uint8_t fw_smem_raw[];
   float* const smem = reinterpret_cast<float*>(fw_smem_raw + ((128u - (smem_u32(fw_smem_raw) & 127u)) & 127u));
   __shared__ __align__(8) uint64_t full_bar[kFwStages], empty_bar[kFwStages];
@@ -110,11 +111,14 @@ sgemm_ffma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (solo && pw != 0) return;
     uint32_t issued = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+    SkWalk<SK> walk;
+    walk.init(sk, num_tiles, num_kb);
+    uint32_t tile, kb0, kb1;
+    while (ok && walk.next(&tile, &kb0, &kb1)) {
       uint32_t tile_m, tile_n;
       mmbo_tile_from_serial(tile, tiles_m, tiles_n, p.wgm, &tile_m, &tile_n);
       const uint32_t m0 = tile_m * kFwBM, n0 = tile_n * kFwBN;
-      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+      for (uint32_t kb = kb0; kb < kb1; ++kb) {
         const uint32_t full = smem_u32(&full_bar[stage]);
         if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, &abort_flag, kFaultWaitEmpty, stage)) {
           ok = false;
@@ -155,7 +159,11 @@ sgemm_ffma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads; m = h * 64 + tx * 4 + e, n = h * 64 + ty * 4 + e
   const float alpha = p.alpha, beta = p.beta;
   const bool use_c = beta != 0.f;
-  for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+  SkWalk<SK> walk;
+  walk.init(sk, num_tiles, num_kb);
+  uint32_t tile, kb0, kb1;
+  constexpr uint32_t kConsumerThreads = kFwConsumerWarps * 32;
+  while (walk.next(&tile, &kb0, &kb1)) {
     uint32_t tile_m, tile_n;
     mmbo_tile_from_serial(tile, tiles_m, tiles_n, p.wgm, &tile_m, &tile_n);
     const uint32_t m0 = tile_m * kFwBM, n0 = tile_n * kFwBN;
@@ -165,7 +173,7 @@ sgemm_ffma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc2[j][i] = 0ull;
 
-    for (uint32_t kb = 0; kb < num_kb; ++kb) {
+    for (uint32_t kb = kb0; kb < kb1; ++kb) {
       if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag, kFaultWaitFull, stage)) return;
       const float* __restrict__ a_s = smem + stage * kFwSlabFloats + tx * 4;
       const float* __restrict__ b_s = smem + (kFwStages + stage) * kFwSlabFloats + ty * 4;
@@ -191,6 +199,42 @@ sgemm_ffma_ws_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
       if (++stage == kFwStages) { stage = 0; phase ^= 1u; }
+    }
+
+    if (SK && kb0 != 0u) {
+      // A later piece of a tile whose first slabs another CTA holds: hand the partial sums over (pair v of
+      // thread t at [(cta * 32 + v) * 256 + t]) and raise this warp's flag.
+      unsigned long long* part = static_cast<unsigned long long*>(sk.partials) + (size_t)blockIdx.x * 32u * kConsumerThreads + tid;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) __stcg(part + (size_t)(j * 4 + i) * kConsumerThreads, (unsigned long long)acc2[j][i]);
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) sk_store_flag(sk.flags + blockIdx.x * kFwConsumerWarps + warp, sk.epoch);
+      continue;
+    }
+    if (SK && kb1 != num_kb) {
+      // First slabs of a tile that continues in the next CTAs' runs: add their partial sums in CTA order.
+      const unsigned long long units = (unsigned long long)num_tiles * num_kb;
+      const uint64_t one2 = pack_f32x2(0x3f800000u, 0x3f800000u);
+      uint32_t have = kb1, jc = blockIdx.x + 1u;
+      while (have < num_kb && jc < gridDim.x) {
+        const unsigned long long run = sk_first_unit(units, jc + 1u, gridDim.x) - sk_first_unit(units, jc, gridDim.x);
+        const uint32_t piece = run < (unsigned long long)(num_kb - have) ? (uint32_t)run : num_kb - have;
+        if (piece != 0u) {
+          if (!sk_wait_flag(sk.flags + jc * kFwConsumerWarps + warp, sk.epoch, &abort_flag, jc)) return;
+          const unsigned long long* part =
+              static_cast<const unsigned long long*>(sk.partials) + (size_t)jc * 32u * kConsumerThreads + tid;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)  // acc + 1 * partial, each half rounded as a scalar add
+              acc2[j][i] = fma_f32x2(one2, (uint64_t)__ldcg(part + (size_t)(j * 4 + i) * kConsumerThreads), acc2[j][i]);
+        }
+        have += piece;
+        ++jc;
+      }
     }
 
     // Write-back: C = beta != 0 ? alpha*acc + beta*C : alpha*acc.

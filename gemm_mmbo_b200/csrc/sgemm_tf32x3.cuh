@@ -338,7 +338,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
       for (int i = 0; i < kTfSums; ++i) sums[i] = 0.f;
       for (uint32_t ch = 0; ok && ch < num_chunks; ++ch, ++chunk_ctr) {
         const uint32_t acc = chunk_ctr & 1u, acc_phase = (chunk_ctr >> 1) & 1u;
-        ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, kFaultWaitTmemFull, acc));
+        ok = mbar_wait_warp(tmem_full_bar(acc), acc_phase, abort_flag, kFaultWaitTmemFull, acc);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t t_warp = tmem_base + ((32u * q) << 16) + acc * TM + col_base;

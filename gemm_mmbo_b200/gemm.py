@@ -260,11 +260,12 @@ def set_workspace(buf, nbytes: int = 0) -> None:
         raise MmboError(rc, "mmbo_set_workspace")
 
 
-def tuning_set(dtype, transA: bool, transB: bool, m: int, n: int, k: int, kernel_id: int) -> None:
-    """Pin the kernel automatic selection uses for one exact problem."""
-    rc = LIB.mmbo_tuning_set(_DTYPES[dtype], int(bool(transA)), int(bool(transB)), m, n, k, kernel_id)
+def tuning_set(dtype, transA: bool, transB: bool, m: int, n: int, k: int, kernel_id: int, split: int = 0) -> None:
+    """Pin the kernel (and, optionally, how the contraction is split: 0 per call, 1 never, 2 always)
+    automatic selection uses for one exact problem."""
+    rc = LIB.mmbo_tuning_set_split(_DTYPES[dtype], int(bool(transA)), int(bool(transB)), m, n, k, kernel_id, split)
     if rc != 0:
-        raise MmboError(rc, "mmbo_tuning_set")
+        raise MmboError(rc, "mmbo_tuning_set_split")
 
 
 def tuning_load(path) -> None:

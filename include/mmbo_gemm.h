@@ -128,7 +128,8 @@ int mmbo_gemm_f16_sharded(int nGpus, int rank, void* ncclComm, int gatherC, int 
  * GPUs over NVLink (ncclAllGather / grouped ncclBroadcast on an internal stream), so the host
  * bridge carries A once per node instead of once per GPU.  B and C blocks go through the same
  * overlapped panel pipeline as mmbo_gemm_f16_host.  Returns when C_block holds the result.
- * Collective: every rank of the communicator must make the call. */
+ * Collective: every rank of the communicator must make the call; a problem with fewer than nGpus
+ * blocks of 256 columns (some rank would own nothing) is refused on every rank (MMBO_ERR_BAD_SHARD). */
 int mmbo_gemm_f16_sharded_host(int nGpus, int rank, void* ncclComm, int transA, int transB, size_t m,
                                size_t n, size_t k, const float* alpha, const void* A, size_t lda,
                                const void* B_block, size_t ldb, const float* beta, void* C_block,
@@ -198,6 +199,12 @@ int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, si
  * gemm_mmbo_b200/autotune.py measures every kernel on a list of sizes and writes such a
  * file (the brute-force sweep of src/gemm/benchmark.cc:92-106, persisted). */
 int mmbo_tuning_set(int dtype, int transA, int transB, size_t m, size_t n, size_t k, int kernelId);
+/* The same with a split mode for the contraction of that problem (0 decided per call, 1 never, 2
+ * always: stream-K in the rows that have it -- fp64 rows 3 and 4, fp32 row 6), the counterpart of a
+ * tuned GlobalSplitU value (src/gemm/ref/vega20_Cijk_Ailk_Bjlk_DB.yaml:69-71).  In a tuning file the
+ * split mode is an optional seventh field of a row.  The option "split_k", when non-zero, wins. */
+int mmbo_tuning_set_split(int dtype, int transA, int transB, size_t m, size_t n, size_t k, int kernelId,
+                          int split);
 int mmbo_tuning_load(const char* path);
 void mmbo_tuning_clear(void);
 

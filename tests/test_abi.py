@@ -186,3 +186,37 @@ def test_strided_batched_rejects_bad_arguments(mm):
     assert LIB.mmbo_gemm_strided_batched(*bad) == -7
     bad = list(ok); bad[17] = 0  # an empty batch is accepted and launches nothing
     assert LIB.mmbo_gemm_strided_batched(*bad) == 0
+
+
+def test_sharded_entry_points_reject_bad_arguments_before_any_launch(mm):
+    """Host-side checks of the multi-GPU entry points (no GPU, no NCCL needed): rank and GPU count, a
+    missing communicator where an exchange is asked for, leading dimensions, and the empty problem."""
+    from gemm_mmbo_b200._lib import LIB
+    one = ctypes.c_float(1.0)
+    a = ctypes.byref(one)
+
+    def sharded(n_gpus, rank, comm, gather, m=512, n=1024, k=64, lda=512, ldb=64, ldc=512):
+        return LIB.mmbo_gemm_f16_sharded(n_gpus, rank, comm, gather, 0, 0, m, n, k, a, BAD, lda, BAD, ldb, a, BAD, ldc, -1, None)
+
+    assert sharded(0, 0, None, 0) == -10
+    assert sharded(2, 2, None, 0) == -10
+    assert sharded(2, -1, None, 0) == -10
+    assert sharded(2, 0, None, 1) == -3          # an exchange needs the caller's communicator
+    assert sharded(2, 1, None, 0, lda=100) == -4
+    assert sharded(2, 1, None, 0, ldb=10) == -5
+    assert sharded(2, 1, None, 0, m=0) == 0      # nothing to do, nothing launched
+    host = LIB.mmbo_gemm_f16_sharded_host
+    assert host(2, 0, None, 0, 0, 512, 1024, 64, a, BAD, 512, BAD, 64, a, BAD, 512, -1) == -3
+    assert host(3, 3, None, 0, 0, 512, 1024, 64, a, BAD, 512, BAD, 64, a, BAD, 512, -1) == -10
+
+
+@pytest.mark.parametrize("cols,world", [(32768, 8), (520, 2), (1024, 2), (8, 4), (4100, 3)])
+def test_shares_of_a_tile_its_columns_on_16_byte_boundaries(mm, cols, world):
+    """The shares of A that the ranks upload (mmbo_gemm_f16_sharded_host): consecutive, complete, and
+    starting on multiples of 8 fp16 columns."""
+    pos = 0
+    for r in range(world):
+        c0, cn = mm.shard_columns(cols, world, r, 8)
+        assert c0 == pos and c0 % 8 == 0
+        pos += cn
+    assert pos == cols
