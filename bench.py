@@ -43,7 +43,10 @@ METRIC = "hgemm_tflops"
 UNIT = "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the N=1 workload, from the ncu capture
 # summarised in profiles/ (a profiler figure cannot be taken inside this run)
-TRAFFIC_8192_NT = {"bytes": 1.805e9, "source": "profiles/hgemm_tcgen05_MT256x256x64_CG2_8192cubed.md"}
+TRAFFIC_8192_NT = {  # by kernel id of the fp16 table
+    6: {"bytes": 1.287e9, "source": "profiles/hgemm_tcgen05_MT512x256x64_CG2_8192cubed.md"},
+    3: {"bytes": 1.805e9, "source": "profiles/hgemm_tcgen05_MT256x256x64_CG2_8192cubed.md"},
+}
 
 
 def parse_args():
@@ -457,10 +460,10 @@ def main():
     peak = peaks["sustained"] if ms > 2000.0 else peaks["burst"]
     achieved = 2.0 * m * ncols * k / (kern_avg * 1e-3) / 1e12
     kid = args.kernel if args.kernel >= 0 else mm.select_kernel("f16", ta, tb, m, ncols, k, A, ra, B, rb, C, m)
-    known_traffic = P == 1 and (m, n, k) == (8192, 8192, 8192) and kid == 3
+    traffic = TRAFFIC_8192_NT.get(kid) if (P == 1 and (m, n, k) == (8192, 8192, 8192)) else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": TRAFFIC_8192_NT["bytes"] if known_traffic else None,
-                "traffic_source": TRAFFIC_8192_NT["source"] if known_traffic else None,
+                "frac": achieved / peak, "traffic": traffic["bytes"] if traffic else None,
+                "traffic_source": traffic["source"] if traffic else None,
                 "algorithmic_bytes": 2.0 * (m * k + k * ncols + m * ncols * (2 if w["beta"] else 1)),
                 "peak_source": f"{peaks['source']} cuBLAS bf16 "
                                f"({'sustained' if ms > 2000.0 else 'burst'}); nominal dense fp16 2250",

@@ -43,6 +43,14 @@
 #include "ptx.cuh"
 #include "raster.h"
 
+// 512-row tiles keep the op(B) operand of a k-step's first UMMA in the tensor core's collector buffer for its
+// second one, which then does not read shared memory for it (measured against a build without it: 8192^3
+// 1412-1444 against 1406 TFLOP/s, seconds-long loops under the power cap 1289 against 1264).  Build with
+// -DMMBO_COLLECTOR_A=0 to compare.
+#ifndef MMBO_COLLECTOR_A
+#define MMBO_COLLECTOR_A 1
+#endif
+
 namespace mmbo {
 
 constexpr int kTileN = 128;  // problem-N extent of a CTA tile = UMMA M
@@ -62,6 +70,11 @@ template <int TM, int STAGES, int CG = 1, int EW = 4, int CSETS = (EW == 8 ? 2 :
 struct HgemmSmem {
   static constexpr int kThreads = 64 + 32 * EW;
   static constexpr int kAopRows = TM / CG;                // rows of op(A) staged by one CTA
+  // One UMMA covers at most 256 rows of op(A).  A 512-row tile is two UMMAs per k-step on the same op(B)
+  // operand, each on one "piece" of op(A): piece h holds this CTA's 128 rows of rows [256h, 256h + 256) of the
+  // tile, so that accumulator columns map to tile rows in order.
+  static constexpr int kPieceRows = TM == 512 ? 128 : kAopRows;
+  static constexpr int kPieces = kAopRows / kPieceRows;
   static constexpr int kBopBytes = kTileN * kBlockK * 2;  // op(B) tile  (UMMA A operand)
   static constexpr int kAopBytes = kAopRows * kBlockK * 2;  // op(A) tile  (UMMA B operand)
   static constexpr int kStageBytes = kBopBytes + kAopBytes;
@@ -142,7 +155,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_c, const HgemmParams p,
                      const __grid_constant__ HgemmPeerMaps peers) {
   using L = HgemmSmem<TM, STAGES, CG, EW, CSETS>;
-  static_assert(TM == 128 || TM == 256, "TM is the UMMA N extent");
+  static_assert(TM == 128 || TM == 256 || (TM == 512 && CG == 2), "128 or 256 rows per UMMA; 512 = two UMMAs per k-step of a CTA pair");
   static_assert(EW == 4 || EW == 8, "one or two epilogue warps per tensor-memory quarter");
   // 64-row chunks of the accumulator each epilogue warp drains per tile
   constexpr uint32_t kChunksPerWarp = (TM / 64) / (EW / 4);
@@ -222,7 +235,9 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int32_t prob = static_cast<int32_t>(locate(tile, &tm_idx, &tn_idx));
         // This CTA's share of the tile: its own 128 columns of C (rows of op(B)^T) and
         // its own TM / CG rows of op(A).
-        const int32_t m0 = static_cast<int32_t>(tm_idx * TM + cta_rank * L::kAopRows);
+        // piece h of op(A): this CTA's kPieceRows rows of the h-th 256-row (or whole) part of the tile
+        const int32_t m0 = static_cast<int32_t>(tm_idx * TM + cta_rank * L::kPieceRows);
+        constexpr int32_t kPieceStep = L::kPieceRows * CG;
         const int32_t n0 = static_cast<int32_t>((tn_idx * CG + cta_rank) * kTileN);
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kFaultWaitEmpty, stage)) {
@@ -246,12 +261,17 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int c = 0; c < kTileN / 64; ++c)  // boxes {64 n, 64 k}
               load(s_bop + c * 8192, &tmap_b, n0 + 64 * c, k0);
           }
-          if constexpr (A_KMAJOR) {
-            load(s_aop, &tmap_a, k0, m0);  // box {64 k, TM / CG m}
-          } else {
 #pragma unroll
-            for (int c = 0; c < L::kAopRows / 64; ++c)  // boxes {64 m, 64 k}
-              load(s_aop + c * 8192, &tmap_a, m0 + 64 * c, k0);
+          for (int h = 0; h < L::kPieces; ++h) {
+            const uint32_t s_piece = s_aop + h * (L::kPieceRows * kBlockK * 2);
+            const int32_t mp = m0 + h * kPieceStep;
+            if constexpr (A_KMAJOR) {
+              load(s_piece, &tmap_a, k0, mp);  // box {64 k, kPieceRows m}
+            } else {
+#pragma unroll
+              for (int c = 0; c < L::kPieceRows / 64; ++c)  // boxes {64 m, 64 k}
+                load(s_piece + c * 8192, &tmap_a, mp + 64 * c, k0);
+            }
           }
           ++issued;
           if (++stage == STAGES) {
@@ -282,7 +302,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ===== UMMA issuer (leader CTA of a pair) =====
     if (lane == 0 && cta_rank == 0) {
-      constexpr uint32_t idesc = make_idesc(0u, B_KMAJOR ? 0u : 1u, A_KMAJOR ? 0u : 1u, kTileN * CG, TM);
+      constexpr uint32_t kUmmaN = TM < 256 ? TM : 256;  // accumulator columns one UMMA writes
+      constexpr uint32_t idesc = make_idesc(0u, B_KMAJOR ? 0u : 1u, A_KMAJOR ? 0u : 1u, kTileN * CG, kUmmaN);
       constexpr uint32_t kStepBop = B_KMAJOR ? 32u : 2048u;  // bytes per UMMA K step
       constexpr uint32_t kStepAop = A_KMAJOR ? 32u : 2048u;
       constexpr uint32_t kLboBop = B_KMAJOR ? 16u : 8192u;
@@ -312,8 +333,19 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t desc_b = make_smem_desc_sw128(s_aop, kLboAop, 1024u);
 #pragma unroll
           for (uint32_t j = 0; j < kBlockK / kUmmaK; ++j) {
-            umma_ss<CG, false>(d_tmem, desc_a + ((j * kStepBop) >> 4), desc_b + ((j * kStepAop) >> 4),
-                               idesc, (kb | j) != 0u ? 1u : 0u);
+#pragma unroll
+            for (uint32_t h = 0; h < (uint32_t)L::kPieces; ++h) {  // one UMMA per 256-row piece, same op(B) operand
+              const uint64_t piece = (uint64_t)((h * (uint32_t)(L::kPieceRows * kBlockK * 2)) >> 4);
+              const uint64_t da = desc_a + ((j * kStepBop) >> 4), db = desc_b + piece + ((j * kStepAop) >> 4);
+              const uint32_t accumulate = (kb | j) != 0u ? 1u : 0u;
+              if constexpr (MMBO_COLLECTOR_A != 0 && L::kPieces == 2 && CG == 2) {
+                // the second UMMA of the pair takes op(B) from the collector buffer
+                if (h == 0) umma_ss_pair_f16_collect_a<false>(d_tmem, da, db, idesc, accumulate);
+                else umma_ss_pair_f16_collect_a<true>(d_tmem + kUmmaN, da, db, idesc, accumulate);
+              } else {
+                umma_ss<CG, false>(d_tmem + h * kUmmaN, da, db, idesc, accumulate);
+              }
+            }
           }
           // frees the stage (in both CTAs of a pair) once these UMMAs have read it
           if constexpr (CG == 2) umma_commit_pair(empty_bar(stage), 3);
@@ -544,29 +576,44 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (c + 1 < kChunksPerWarp) load_chunk(c + 1, racc[2 * (kPb ^ 1u)], racc[2 * (kPb ^ 1u) + 1]);
           else release_accumulator();  // this warp's part of the accumulator is read: hand it back
         }
+        // alpha * acc (+ beta * old C) on pairs of fp32 values (fma.rn.f32x2: one instruction per pair, each
+        // half rounded as the scalar operation would be), then one conversion per pair.  The two run-time
+        // choices (old C or not, alpha == 1 or not) are made once per chunk, outside the unrolled loops:
+        // with short contractions the epilogue warps are bound by instruction issue.
+        auto convert = [&](auto with_c, auto scale) {
+          constexpr bool kWithC = decltype(with_c)::value, kScale = decltype(scale)::value;
+          uint8_t* const row = gbuf + lane * 128u;
+          const uint32_t x = lane & 7u;
 #pragma unroll
-        for (uint32_t h = 0; h < 2; ++h) {
-          const uint32_t(&r)[32] = racc[kEarlyDrain ? 2 * c + h : 2 * kPb + h];
+          for (uint32_t h = 0; h < 2; ++h) {
+            const uint32_t(&r)[32] = racc[kEarlyDrain ? 2 * c + h : 2 * kPb + h];
 #pragma unroll
-          for (uint32_t jj = 0; jj < 4; ++jj) {
-            const uint32_t j = 4u * h + jj;  // 16-byte chunk of the 128-byte row
-            uint8_t* addr = gbuf + lane * 128u + ((j ^ (lane & 7u)) << 4);
-            // alpha * acc (+ beta * old C) on pairs of fp32 values (fma.rn.f32x2: one instruction per
-            // pair, each half rounded as the scalar operation would be), then one conversion per pair
-            uint4 out;
-            uint32_t* po = reinterpret_cast<uint32_t*>(&out);
-            uint4 old = make_uint4(0u, 0u, 0u, 0u);
-            if (load_c) old = *reinterpret_cast<const uint4*>(addr);
-            const uint32_t* oldw = reinterpret_cast<const uint32_t*>(&old);
+            for (uint32_t jj = 0; jj < 4; ++jj) {
+              const uint32_t j = 4u * h + jj;  // 16-byte piece of the 128-byte row
+              uint4* const addr = reinterpret_cast<uint4*>(row + ((j ^ x) << 4));
+              uint4 out, old;
+              uint32_t* po = reinterpret_cast<uint32_t*>(&out);
+              if constexpr (kWithC) old = *addr;
+              const uint32_t* oldw = reinterpret_cast<const uint32_t*>(&old);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              uint64_t v = pack_f32x2(r[8 * jj + 2 * e], r[8 * jj + 2 * e + 1]);
-              if (!alpha_one) v = mul_f32x2(alpha2, v);
-              if (load_c) v = fma_f32x2(beta2, half2_to_f32x2(oldw[e]), v);
-              po[e] = f32x2_to_half2(v);
+              for (int e = 0; e < 4; ++e) {
+                uint64_t v = pack_f32x2(r[8 * jj + 2 * e], r[8 * jj + 2 * e + 1]);
+                if constexpr (kScale) v = mul_f32x2(alpha2, v);
+                if constexpr (kWithC) v = fma_f32x2(beta2, half2_to_f32x2(oldw[e]), v);
+                po[e] = f32x2_to_half2(v);
+              }
+              *addr = out;
             }
-            *reinterpret_cast<uint4*>(addr) = out;
           }
+        };
+        using Yes = std::true_type;
+        using No = std::false_type;
+        if (load_c) {
+          if (alpha_one) convert(Yes{}, No{});
+          else convert(Yes{}, Yes{});
+        } else {
+          if (alpha_one) convert(No{}, No{});
+          else convert(No{}, Yes{});
         }
         if (tracer && c == 0) trace_stamp(p.trace, local_tile, 11);  // chunk 0 written to staging
         if (c_tma && p.c_mc != nullptr) {

@@ -52,6 +52,7 @@ static const KernelRow kF16Rows[] = {
     {"hgemm_tcgen05_MT256x256x64_S6_CG2_WG192_WGM08", 256, 256, 192, 64, 6, 2, 8, 1},
     {"hgemm_tcgen05_MT256x256x64_S3_CG2_WG320_WGM08", 256, 256, 320, 64, 3, 2, 8, 1},
     {"hgemm_tcgen05_MT256x256x64_S5_CG2_WG320_WGM08", 256, 256, 320, 64, 5, 2, 8, 1},
+    {"hgemm_tcgen05_MT512x256x64_S4_CG2_WG192_WGM08", 512, 256, 192, 64, 4, 2, 8, 1},
 };
 // fp64 rows (the reference's own dtype).
 static const KernelRow kF64Rows[] = {
@@ -446,10 +447,12 @@ static int launch_sgemm_ffma_ws(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   // Eight CTAs per SM in the grid, two resident: as CTAs finish their few tiles the hardware starts the
   // next ones, which balances the end of the launch (4096^3: 61.1 TFLOP/s against 52.3 with 2 per SM).
   unsigned grid = (unsigned)std::min(tiles, (size_t)8 * (size_t)sm_count());
-  // Few tiles: stream-K over the two resident CTAs per SM instead (all of them run at once, which the
-  // flag hand-over between CTAs relies on).
+  // Few tiles (fewer than two per resident CTA): stream-K over the two resident CTAs per SM instead (all of
+  // them run at once, which the flag hand-over between CTAs relies on): 1024^3 22.9 -> 33.0 TFLOP/s, 2048^3
+  // 49.3 -> 52.8.  With more tiles the oversubscribed grid already balances the end of the launch and the
+  // split only costs (4096^3 NN / NT / TN: 58.3 / 61.1 / 54.9 without, 55.6 / 59.3 / 52.4 with).
   SkPlan plan{false, 0, 0, 0};
-  if (tiles < (size_t)8 * (size_t)sm_count())
+  if (tiles < (size_t)4 * (size_t)sm_count())
     plan = plan_stream_k(tiles, (g.k + kFwBK - 1) / kFwBK, (size_t)2 * (size_t)sm_count(), (size_t)kFwBM * kFwBN * 4,
                          kFwConsumerWarps, g.batch);
   StreamK sk;
@@ -578,7 +581,7 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   constexpr auto SW = CU_TENSOR_MAP_SWIZZLE_128B;
   // op(A): K-major when transposed (stored k x m), MN-major otherwise (stored m x k).
   if (g.transA)
-    rc = make_map(&ta, F16, 2, g.A, g.k, g.m, g.lda, kBlockK, TM / CG, SW, g.batch, g.sA);
+    rc = make_map(&ta, F16, 2, g.A, g.k, g.m, g.lda, kBlockK, HgemmSmem<TM, STAGES, CG, EW, CSETS>::kPieceRows, SW, g.batch, g.sA);
   else
     rc = make_map(&ta, F16, 2, g.A, g.m, g.k, g.lda, 64, kBlockK, SW, g.batch, g.sA);
   if (rc) return rc;
@@ -847,7 +850,9 @@ static int select_f32(const GemmArgs& g) {
   const double work = (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
   if (work >= 512.0 * 512.0 * 512.0 && !exact) {
     const uint64_t big_pairs = (uint64_t)((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch;
-    if (big_pairs >= 2ull * (uint64_t)(sm_count() / 2)) return 5;  // 256 x 256 tiles, two waves or more
+    // 256 x 256 pair tiles from 32 of them on (measured by the autotuner: 2048^3 173 against 134 TFLOP/s for the
+    // 128 x 256 row, 2368^3 148 / 135, 3072^3 231 / 178, 1536 x 2048 x 384 73 / 63)
+    if (big_pairs >= 32) return 5;
     const uint64_t pair_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 255) / 256) * g.batch;
     return pair_tiles >= (uint64_t)(sm_count() / 2) ? 3 : 4;
   }
@@ -877,12 +882,20 @@ static int select_f16(const GemmArgs& g) {
   const double s1 = 0.80 * eff(t1, sms) * fill(t1, 256, 128);
   const double s2 = 0.70 * eff(t2, sms) * fill(t2, 128, 128);
   const double s3 = 1.00 * eff(t3, sms / 2) * fill(t3, 256, 256);
+  // 512-row pair tiles: 25 % less operand staging per flop (8192^3: 1404 against 1358 TFLOP/s; seconds-long loops
+  // under the power cap: 1306 against 1257, at a higher clock), but a single accumulator, so the epilogue is
+  // not hidden: only for long contractions.
+  const uint64_t t6 = nb * ((g.m + 511) / 512) * ((g.n + 255) / 256);
+  const double s6 = 1.03 * eff(t6, sms / 2) * fill(t6, 512, 256);
+  if (g.k >= 4096 && s6 >= s3 && s6 >= s1 && s6 >= s2) return 6;
   // Short contractions are bound by the epilogue: the rows with eight epilogue warps win there.  Up to
   // k = 512 the one that requests the old C a whole tile ahead into a second set of staging buffers
   // (three operand stages); up to k = 2048 the one with five stages and an L2 prefetch of the next tile's
   // C instead (8192 x 8192 x 1024, beta = 1: 131 against 137 us; x 2048: 229 against 248 us; x 512: 92
   // against 89 us); the six-stage row with four epilogue warps beyond.
-  if (s3 >= s1 && s3 >= s2) return g.k <= 512 ? 4 : g.k <= 2048 ? 5 : 3;
+  // Without old C to fetch (beta == 0) the second staging set buys nothing and the five-stage row wins at
+  // every short k (8192 x 8192 x 256: 49.8 against 51.4 us).
+  if (s3 >= s1 && s3 >= s2) return g.k <= 2048 ? ((g.k <= 512 && g.beta != 0.0f) ? 4 : 5) : 3;
   return s1 >= s2 ? 1 : 2;
 }
 
@@ -1118,6 +1131,7 @@ static int run_f16(const GemmArgs& g_in, int id, cudaStream_t st) {
     case 3: rc = launch_hgemm_tcgen05<256, 6, 2>(g, wgm_of(kF16Rows[3]), st); break;
     case 4: rc = launch_hgemm_tcgen05<256, 3, 2, 8>(g, wgm_of(kF16Rows[4]), st); break;
     case 5: rc = launch_hgemm_tcgen05<256, 5, 2, 8, 1>(g, wgm_of(kF16Rows[5]), st); break;
+    case 6: rc = launch_hgemm_tcgen05<512, 4, 2, 4>(g, wgm_of(kF16Rows[6]), st); break;
     default: rc = MMBO_ERR_BAD_KERNEL_ID;
   }
   if (scratch_used) {
@@ -1636,7 +1650,7 @@ int mmbo_kernel_params(int dtype, int kernelId, int out[8]) {
 int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, size_t k, const void* A,
                        size_t lda, const void* B, size_t ldb, const void* C, size_t ldc) {
   MMBO_API_LOCK();
-  GemmArgs g{transA, transB, m, n, k, A, B, const_cast<void*>(C), lda, ldb, ldc, 1.f, 0.f};
+  GemmArgs g{transA, transB, m, n, k, A, B, const_cast<void*>(C), lda, ldb, ldc, 1.f, 1.f};  // (as for beta != 0)
   const float one = 1.f;
   int rc = validate(g, &one, &one);
   if (rc) return rc;

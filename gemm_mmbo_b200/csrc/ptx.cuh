@@ -381,6 +381,32 @@ __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64
         : "memory");
 }
 
+// CTA-pair fp16 UMMA that keeps its A operand in the tensor core's collector buffer (FILL) for the next
+// UMMA, which takes it from there instead of reading shared memory again (LASTUSE) -- for consecutive UMMAs
+// on the same A descriptor (a tile taller than one UMMA: same op(B) operand, next piece of op(A)).
+template <bool LASTUSE>
+__device__ __forceinline__ void umma_ss_pair_f16_collect_a(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                          uint32_t idesc, uint32_t accumulate) {
+  if constexpr (!LASTUSE)
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16.collector::a::fill [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16.collector::a::lastuse [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // Arrive on an mbarrier of this CTA once every UMMA issued so far by this thread has
 // finished (implies tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void umma_commit(uint32_t bar) {

@@ -185,7 +185,9 @@ int mmbo_num_kernels(int dtype);
 const char* mmbo_kernel_name(int dtype, int kernelId);
 int mmbo_kernel_params(int dtype, int kernelId, int out[8]);
 /* Kernel id that MMBO_KERNEL_AUTO resolves to for these operands (same checks as the
- * gemm call; A, B, C may be any pointers with the alignment of the real ones). */
+ * gemm call; A, B, C may be any pointers with the alignment of the real ones).  The answer is the
+ * one for beta != 0; with beta == 0 a call may take the fp16 row with more operand stages instead
+ * of the one with a second set of staging buffers for old C. */
 int mmbo_select_kernel(int dtype, int transA, int transB, size_t m, size_t n, size_t k,
                        const void* A, size_t lda, const void* B, size_t ldb, const void* C,
                        size_t ldc);
