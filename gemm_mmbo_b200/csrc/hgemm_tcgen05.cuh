@@ -50,6 +50,23 @@
 #ifndef MMBO_COLLECTOR_A
 #define MMBO_COLLECTOR_A 1
 #endif
+// Probe builds only (-DMMBO_TRACE_KB=1): extra trace stamps inside the k loops of the producer and the issuer
+// (slot 13/14: first/last operand stage of the tile has arrived; slot 15: the producer got the tile's first
+// free stage).  Off in the shipped library: a branch in the issuer's loop costs throughput.
+#ifndef MMBO_TRACE_KB
+#define MMBO_TRACE_KB 0
+#endif
+// Probe build 3: per-role accounting of the cycles spent in barrier waits (totals written at the end of each
+// role's loop to slots of trace tile 62).
+#if MMBO_TRACE_KB == 3
+#define MMBO_ACCT_BEGIN() const long long acct_t_ = clock64()
+#define MMBO_ACCT_END(var) var += clock64() - acct_t_
+#define MMBO_ACCT_OUT(slot, v) if (p.trace != nullptr && blockIdx.x == 0) p.trace[62 * 16 + (slot)] = (unsigned long long)(v)
+#else
+#define MMBO_ACCT_BEGIN()
+#define MMBO_ACCT_END(var)
+#define MMBO_ACCT_OUT(slot, v)
+#endif
 
 namespace mmbo {
 
@@ -145,6 +162,9 @@ __device__ __forceinline__ void cluster_sync_all() {
 // 0-7 epilogue, 8-15 issuer).  The counterpart of the reference's #ifdef DEBUG prints
 // (src/gemm/driver.h:38-55), for the device side.
 __device__ __forceinline__ void trace_stamp(unsigned long long* trace, uint32_t tile_slot, uint32_t ev) {
+#if MMBO_TRACE_KB >= 2
+  if (tile_slot != 63u) return;  // probe build: only the launch-level stamps (kernel entry, loops done, exit)
+#endif
   if (trace != nullptr && blockIdx.x == 0 && tile_slot < 64u) trace[tile_slot * 16u + ev] = clock64();
 }
 
@@ -172,6 +192,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+#if MMBO_TRACE_KB
+  if (threadIdx.x == 0) {
+    trace_stamp(p.trace, 63u, 0);
+    if (p.trace != nullptr && blockIdx.x == 0) p.trace[63 * 16 + 6] = global_timer_ns();
+  }
+#endif
 
   const uint32_t bar_base = smem_base + L::kBarOffset;
   auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
@@ -223,6 +249,9 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if constexpr (CG == 2) cluster_sync_all();  // peer's barriers and tensor memory are ready
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
+#if MMBO_TRACE_KB
+  if (threadIdx.x == 0) trace_stamp(p.trace, 63u, 1);
+#endif
 
   // ------------------------------------------------------------------ roles ---------
   if (warp == 0) {
@@ -230,6 +259,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, issued = 0;
       bool ok = true;
+      [[maybe_unused]] long long w_empty = 0;
+      [[maybe_unused]] const long long loop_t0 = clock64();
       for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers) {
         uint32_t tm_idx, tn_idx;
         const int32_t prob = static_cast<int32_t>(locate(tile, &tm_idx, &tn_idx));
@@ -240,10 +271,15 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         constexpr int32_t kPieceStep = L::kPieceRows * CG;
         const int32_t n0 = static_cast<int32_t>((tn_idx * CG + cta_rank) * kTileN);
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          MMBO_ACCT_BEGIN();
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kFaultWaitEmpty, stage)) {
             ok = false;
             break;
           }
+          MMBO_ACCT_END(w_empty);
+#if MMBO_TRACE_KB
+          if (kb == 0) trace_stamp(p.trace, (tile - walker) / num_walkers, 15);
+#endif
           // Completion is counted on the leader's barrier, which expects both CTAs' bytes.
           const uint32_t bar = (CG == 2) ? mapa_shared(full_bar(stage), 0u) : full_bar(stage);
           const uint32_t s_bop = smem_base + stage * L::kStageBytes;
@@ -280,6 +316,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+      MMBO_ACCT_OUT(0, clock64() - loop_t0);
+      MMBO_ACCT_OUT(1, w_empty);
       if (!ok && cta_rank == 0) {
         // Unwind: let every copy this thread issued land before the CTA's shared
         // memory is released.  A stage already consumed reports complete at once.
@@ -310,23 +348,37 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       constexpr uint32_t kLboAop = A_KMAJOR ? 16u : 8192u;
       uint32_t stage = 0, phase = 0, local_tile = 0;
       bool ok = true;
+      [[maybe_unused]] long long w_acc = 0, w_full = 0;
+      [[maybe_unused]] const long long loop_t0 = clock64();
       for (uint32_t tile = walker; ok && tile < num_tiles; tile += num_walkers, ++local_tile) {
         const uint32_t acc = local_tile % kAccs;
         const uint32_t acc_phase = (local_tile / kAccs) & 1u;
         trace_stamp(p.trace, local_tile, 8);
-        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, kFaultWaitTmemEmpty, acc)) {
-          ok = false;
-          break;
+        {
+          MMBO_ACCT_BEGIN();
+          if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, kFaultWaitTmemEmpty, acc)) {
+            ok = false;
+            break;
+          }
+          MMBO_ACCT_END(w_acc);
         }
         trace_stamp(p.trace, local_tile, 9);
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TM;
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, kFaultWaitFull, stage)) {
-            ok = false;
-            break;
+          {
+            MMBO_ACCT_BEGIN();
+            if (!mbar_wait(full_bar(stage), phase, abort_flag, kFaultWaitFull, stage)) {
+              ok = false;
+              break;
+            }
+            MMBO_ACCT_END(w_full);
           }
           tcgen05_fence_after();
+#if MMBO_TRACE_KB
+          if (kb == 0) trace_stamp(p.trace, local_tile, 13);
+          if (kb + 1 == num_kb) trace_stamp(p.trace, local_tile, 14);
+#endif
           const uint32_t s_bop = smem_base + stage * L::kStageBytes;
           const uint32_t s_aop = s_bop + L::kBopBytes;
           const uint64_t desc_a = make_smem_desc_sw128(s_bop, kLboBop, 1024u);
@@ -361,6 +413,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           else umma_commit(tmem_full_bar(acc));
         }
       }
+#if MMBO_TRACE_KB
+      trace_stamp(p.trace, 63u, 2);
+#endif
+      MMBO_ACCT_OUT(2, clock64() - loop_t0);
+      MMBO_ACCT_OUT(3, w_acc);
+      MMBO_ACCT_OUT(4, w_full);
     }
     __syncwarp();
   } else {
@@ -392,6 +450,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     constexpr uint32_t kSets = kCAhead ? (uint32_t)L::kBufsPerWarp / kSetChunks : 1u;
     constexpr uint32_t kAhead = kSets - 1u;
     constexpr int kStoresPending = (int)(kSets * kSetChunks) - 1;  // bulk groups that may still be reading other buffers
+    [[maybe_unused]] long long w_tfull = 0, w_cload = 0, w_store = 0, w_rel = 0;
+    [[maybe_unused]] const long long loop_t0 = clock64();
     uint32_t c_in_flight = 0;  // bit b: a load into buffer b of this warp has been requested and not yet awaited
     auto request_c = [&](uint32_t t, uint32_t set) {  // whole warp; lane 0 issues: chunks of tile t into buffer set `set`
       uint32_t tm, tn;
@@ -452,7 +512,11 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       // One lane polls (with back-off once the wait has become a long one); the outcome is warp-uniform so
       // that the aligned tcgen05 instructions below always run with a converged warp.
-      ok = mbar_wait_warp(tmem_full_bar(acc), acc_phase, abort_flag, kFaultWaitTmemFull, acc);
+      {
+        MMBO_ACCT_BEGIN();
+        ok = mbar_wait_warp(tmem_full_bar(acc), acc_phase, abort_flag, kFaultWaitTmemFull, acc);
+        MMBO_ACCT_END(w_tfull);
+      }
       if (!ok) break;
       if (tracer) trace_stamp(p.trace, local_tile, 2);
       tcgen05_fence_after();
@@ -502,9 +566,13 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           load_piece(3);
         } else {
 #pragma unroll
-          for (uint32_t i = 0; i < 2 * kChunksPerWarp; ++i) load_piece(i);
-          tmem_ld_wait();
-          release_accumulator();
+          {
+            MMBO_ACCT_BEGIN();
+            for (uint32_t i = 0; i < 2 * kChunksPerWarp; ++i) load_piece(i);
+            tmem_ld_wait();
+            release_accumulator();
+            MMBO_ACCT_END(w_rel);
+          }
         }
         if (tracer) trace_stamp(p.trace, local_tile, 3);
         if (kCAhead && c_tma && use_c && tile + kAhead * num_walkers < num_tiles) {
@@ -533,8 +601,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (c_tma) {
           if (!use_c || c >= 2u) {
             // The store last issued from this buffer (kStoresPending + 1 chunks ago) must have read it.
-            if (lane == 0) tma_store_wait_read<kStoresPending>();
-            __syncwarp();
+            {
+              MMBO_ACCT_BEGIN();
+              if (lane == 0) tma_store_wait_read<kStoresPending>();
+              __syncwarp();
+              MMBO_ACCT_END(w_store);
+            }
             if (load_c) c_in_flight |= 1u << (kSetChunks * set + b);
             if (load_c && lane == 0) {  // chunks beyond the two requested up front
               mbar_expect_tx(cload_bar(epi_w, kSetChunks * set + b), kEpiBufBytes);
@@ -562,9 +634,11 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         if (c_tma && load_c) {
+          MMBO_ACCT_BEGIN();
           if (!mbar_wait(cload_bar(epi_w, kSetChunks * set + b), (cphase >> (kSetChunks * set + b)) & 1u, abort_flag,
                          kFaultWaitCLoad, epi_w))
             ok = false;
+          MMBO_ACCT_END(w_cload);
           cphase ^= 1u << (kSetChunks * set + b);
           c_in_flight &= ~(1u << (kSetChunks * set + b));
         }
@@ -688,7 +762,20 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+#if MMBO_TRACE_KB
+    if (warp == 2u && lane == 0u) trace_stamp(p.trace, 63u, 3);
+#endif
+    if (warp == 2u && lane == 0u) {
+      MMBO_ACCT_OUT(5, clock64() - loop_t0);
+      MMBO_ACCT_OUT(6, w_tfull);
+      MMBO_ACCT_OUT(7, w_cload);
+      MMBO_ACCT_OUT(8, w_store);
+      MMBO_ACCT_OUT(9, w_rel);
+    }
     if (lane == 0) tma_store_wait_all<0>();
+#if MMBO_TRACE_KB
+    if (warp == 2u && lane == 0u) trace_stamp(p.trace, 63u, 4);
+#endif
   }
 
   // ------------------------------------------------------------------ teardown ------
@@ -701,6 +788,12 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tcgen05_fence_after();
     tmem_dealloc<CG>(tmem_base, kTmemCols);
   }
+#if MMBO_TRACE_KB
+  if (threadIdx.x == 0) {
+    trace_stamp(p.trace, 63u, 5);
+    if (p.trace != nullptr && blockIdx.x == 0) p.trace[63 * 16 + 7] = global_timer_ns();
+  }
+#endif
 }
 
 }  // namespace mmbo

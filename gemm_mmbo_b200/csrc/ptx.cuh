@@ -78,10 +78,20 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Arrive on a barrier of another CTA of the cluster (address from mapa).
+// Arrive on a barrier of another CTA of the cluster (address from mapa).  The arrive carries the default
+// CTA-scope release: what it hands over here is tensor memory, whose reads are ordered by tcgen05.wait::ld and
+// tcgen05.fence::before_thread_sync, not generic memory.  (A cluster-scope release makes the thread wait for all
+// of its memory traffic in flight -- measured: ~1000 cycles per arrive, 1500-2900 with TMA stores outstanding,
+// which put every tile's release behind the previous tile's stores.)  -DMMBO_RELEASE_CLUSTER=1 restores it.
+#ifndef MMBO_RELEASE_CLUSTER
+#define MMBO_RELEASE_CLUSTER 0
+#endif
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
-               : "memory");
+#if MMBO_RELEASE_CLUSTER
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+#else
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+#endif
 }
 
 __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta_rank) {
