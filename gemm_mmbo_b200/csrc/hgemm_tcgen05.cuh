@@ -121,6 +121,7 @@ struct HgemmParams {
                               // batch * tiles_m * tiles_n tiles, problem index slowest
   unsigned long long c_batch_stride;  // elements between the C of consecutive problems (plain epilogue)
   uint32_t wgm;               // work-group-mapping width (tile columns per block)
+  MmboTileWalk walk;          // the same walk with its divisions precomputed (mmbo_tile_walk_make(tiles_m, tiles_n, wgm))
   float alpha, beta;
   __half* c;       // C and its leading dimension, for the epilogue without TMA
   uint32_t ldc;
@@ -216,8 +217,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // tile id of the walk -> (tile row, tile column, problem of the batch)
   const bool batched = p.batch > 1u;  // 3-D tensor maps; single problems keep the 2-D forms
   auto locate = [&](uint32_t tile, uint32_t* tm, uint32_t* tn) -> uint32_t {
-    const uint32_t prob = batched ? tile / tiles_per_problem : 0u;  // (no division on the single-problem path)
-    mmbo_tile_from_serial(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, p.wgm, tm, tn);
+    const uint32_t prob = batched ? mmbo_fastdiv(tile, p.walk.by_problem) : 0u;
+    mmbo_tile_walk_locate(p.walk, tile - prob * tiles_per_problem, tm, tn);
     return prob;
   };
 

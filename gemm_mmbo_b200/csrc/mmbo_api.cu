@@ -619,6 +619,7 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   p.batch = (uint32_t)g.batch;
   p.c_batch_stride = g.sC;
   p.wgm = wgm;
+  p.walk = mmbo_tile_walk_make(p.tiles_m, p.tiles_n, wgm);
   p.alpha = g.alpha; p.beta = g.beta;
   p.c = static_cast<__half*>(g.C); p.ldc = (uint32_t)g.ldc; p.c_tma = c_tma ? 1u : 0u;
   p.c_mc = nullptr;
@@ -679,6 +680,7 @@ static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float*
   p.batch = (uint32_t)g.batch;
   p.c_batch_stride = g.sC;
   p.wgm = wgm; p.alpha = g.alpha; p.beta = g.beta;
+  p.walk = mmbo_tile_walk_make(p.tiles_m, p.tiles_n, wgm);
   p.c = static_cast<float*>(g.C); p.ldc = (uint32_t)g.ldc; p.c_tma = c_tma ? 1u : 0u;
   p.chunk = settings().tf32_chunk;
   const uint64_t tiles = (uint64_t)p.tiles_m * p.tiles_n * g.batch;

@@ -147,6 +147,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // lane the ordering a wait of its own would have given.  The result is warp-uniform.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                                unsigned int fault_code, unsigned int detail) {
+  // Fast path: the phase has usually completed already when an epilogue warp gets here (it is the slower
+  // side with short contractions): all lanes poll once, and agree.
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
   uint32_t ok = 1u;
   if ((threadIdx.x & 31u) == 0u) ok = mbar_wait(bar, parity, abort_flag, fault_code, detail) ? 1u : 0u;
   ok = __shfl_sync(0xffffffffu, ok, 0);

@@ -124,6 +124,7 @@ struct TfParams {
   uint32_t batch;                     // problems of a strided batch; the walk covers batch * tiles_m * tiles_n tiles
   unsigned long long c_batch_stride;  // elements between the C of consecutive problems (plain epilogue)
   uint32_t wgm;
+  MmboTileWalk walk;  // the walk with its divisions precomputed (mmbo_tile_walk_make(tiles_m, tiles_n, wgm))
   float alpha, beta;
   float* c;        // used by the plain epilogue
   uint32_t ldc;
@@ -161,8 +162,8 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
   const uint32_t num_kb = (p.k + kTfBlockK - 1) / kTfBlockK;
   const bool batched = p.batch > 1u;  // 3-D tensor maps; single problems keep the 2-D forms
   auto locate = [&](uint32_t tile, uint32_t* tm, uint32_t* tn) -> uint32_t {
-    const uint32_t prob = tile / tiles_per_problem;
-    mmbo_tile_from_serial(tile - prob * tiles_per_problem, p.tiles_m, p.tiles_n, p.wgm, tm, tn);
+    const uint32_t prob = batched ? mmbo_fastdiv(tile, p.walk.by_problem) : 0u;
+    mmbo_tile_walk_locate(p.walk, tile - prob * tiles_per_problem, tm, tn);
     return prob;
   };
 
