@@ -73,7 +73,7 @@ namespace mmbo {
 constexpr int kTileN = 128;  // problem-N extent of a CTA tile = UMMA M
 constexpr int kBlockK = 64;  // fp16 elements per stage along K = one 128-byte swizzle row
 constexpr int kUmmaK = 16;   // K extent of one kind::f16 UMMA
-constexpr int kEpiBufBytes = 32 * 128;  // 32 C columns x 64 rows of fp16, per warp buffer
+constexpr int kEpiBufBytesMax = 32 * 128;  // 32 C columns x 64 rows of fp16: the larger of the two staging buffer sizes
 
 // CG = CTAs cooperating on one UMMA (cta_group): 1, or 2 for a CTA pair that shares a
 // 256-lane accumulator; each CTA of a pair stages its own 128 rows of op(B) and its own
@@ -101,7 +101,13 @@ struct HgemmSmem {
   // tile ahead while this tile's set is still in use.
   static constexpr int kCSets = CSETS;
   static constexpr int kBufsPerWarp = 2 * kCSets;
-  static constexpr int kEpiBytes = EW * kBufsPerWarp * kEpiBufBytes;
+  // Rows of C per epilogue chunk (a chunk = these rows x the warp's 32 columns, one staging buffer, one TMA
+  // load of old C and one TMA store): 64 (128-byte staging rows, 128-byte swizzle), or 32 (64-byte rows, 64-byte
+  // swizzle) where a 512-row tile gets eight epilogue warps -- half-size buffers keep their double buffering
+  // inside the 32 KB that four warps with 64-row chunks take, next to four 48 KB operand stages.
+  static constexpr int kChunkRows = (TM == 512 && EW == 8) ? 32 : 64;
+  static constexpr int kBufBytes = 32 * kChunkRows * 2;
+  static constexpr int kEpiBytes = EW * kBufsPerWarp * kBufBytes;
   static constexpr int kBarOffset = kEpiOffset + kEpiBytes;
   // Accumulators in tensor memory (512 columns): two of 256 columns, or four of 128 -- with short
   // contractions the deeper queue keeps the UMMA issuer from ever waiting for the epilogue.
@@ -179,7 +185,14 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   static_assert(TM == 128 || TM == 256 || (TM == 512 && CG == 2), "128 or 256 rows per UMMA; 512 = two UMMAs per k-step of a CTA pair");
   static_assert(EW == 4 || EW == 8, "one or two epilogue warps per tensor-memory quarter");
   // 64-row chunks of the accumulator each epilogue warp drains per tile
-  constexpr uint32_t kChunksPerWarp = (TM / 64) / (EW / 4);
+  constexpr uint32_t kCR = L::kChunkRows;              // rows of C per chunk
+  constexpr uint32_t kEpiBufBytes = L::kBufBytes;      // one staging buffer
+  constexpr uint32_t kRowPieces = kCR / 8u;            // 16-byte pieces per staging row (one C column of a chunk)
+  constexpr uint32_t kLdPerChunk = kCR / 32u;          // 32-column tensor-memory loads per chunk
+  constexpr uint32_t kChunksPerWarp = (TM / kCR) / (EW / 4);
+  // 16-byte piece j of staging row t lives at piece swz(j, t): the TMA swizzle of the C tensor map (128-byte
+  // rows: j ^ (t & 7); 64-byte rows: j ^ ((t >> 1) & 3)).
+  auto swz = [](uint32_t j, uint32_t t) -> uint32_t { return kCR == 64u ? (j ^ (t & 7u)) : (j ^ ((t >> 1) & 3u)); };
   static_assert(kChunksPerWarp >= 1, "tile too narrow for this many epilogue warps");
   static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair per UMMA");
   constexpr uint32_t kAccs = L::kAccs;
@@ -427,7 +440,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // kChunksPerWarp 64-row chunks of them (all of them with 4 warps, half with 8) =====
     const uint32_t q = warp & 3u;
     const uint32_t epi_w = warp - 2u;
-    const uint32_t col_base = (epi_w >> 2) * kChunksPerWarp * 64u;  // first accumulator column of this warp
+    const uint32_t col_base = (epi_w >> 2) * kChunksPerWarp * kCR;  // first accumulator column of this warp
     const uint32_t warp_buf_base = smem_base + L::kEpiOffset + epi_w * L::kBufsPerWarp * kEpiBufBytes;
     uint8_t* warp_buf_gen = smem_gen + L::kEpiOffset + epi_w * L::kBufsPerWarp * kEpiBufBytes;
     const bool use_c = (p.beta != 0.0f);
@@ -460,7 +473,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t mr = tm * TM + col_base, nc = (tn * CG + cta_rank) * kTileN + 32u * q;
 #pragma unroll
       for (uint32_t c = 0; c < kSetChunks; ++c) {
-        const uint32_t mrow0 = mr + 64u * c;
+        const uint32_t mrow0 = mr + kCR * c;
         if (mrow0 < p.m && nc < p.n) {
           c_in_flight |= 1u << (kSetChunks * set + c);
           if (lane == 0) {
@@ -508,8 +521,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t nm0 = nm * TM + col_base, nn0 = (nn * CG + cta_rank) * kTileN + 32u * q;
 #pragma unroll
         for (uint32_t c = 0; c < kChunksPerWarp; ++c)
-          if (nm0 + 64u * c < p.m && nn0 < p.n)
-            tma_prefetch_l2_tile(batched, &tmap_c, static_cast<int32_t>(nm0 + 64u * c), static_cast<int32_t>(nn0), npr);
+          if (nm0 + kCR * c < p.m && nn0 < p.n)
+            tma_prefetch_l2_tile(batched, &tmap_c, static_cast<int32_t>(nm0 + kCR * c), static_cast<int32_t>(nn0), npr);
       }
       // One lane polls (with back-off once the wait has become a long one); the outcome is warp-uniform so
       // that the aligned tcgen05 instructions below always run with a converged warp.
@@ -544,13 +557,14 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t racc[kEarlyDrain ? 2 * kChunksPerWarp : 4][32];
       auto load_chunk = [&](const uint32_t c, uint32_t (&lo)[32], uint32_t (&hi)[32]) {
         if (drain) {
-          tmem_ld_32x32(t_warp + 64u * c, lo);
-          tmem_ld_32x32(t_warp + 64u * c + 32u, hi);
+          tmem_ld_32x32(t_warp + kCR * c, lo);
+          if constexpr (kLdPerChunk == 2) tmem_ld_32x32(t_warp + kCR * c + 32u, hi);
         } else {
 #pragma unroll
           for (int e = 0; e < 32; ++e) lo[e] = hi[e] = 0u;
         }
       };
+      static_assert(kCR == 64u || !(kChunksPerWarp <= 2), "32-row chunks use the double-buffered drain");
       if constexpr (kEarlyDrain) {
         auto load_piece = [&](uint32_t i) {
           if (drain) tmem_ld_32x32(t_warp + 32u * i, racc[i]);
@@ -590,7 +604,7 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t b = c & 1u;
         const uint32_t sbuf = buf_base + b * kEpiBufBytes;
         uint8_t* gbuf = buf_gen + b * kEpiBufBytes;
-        const uint32_t mrow0 = m0 + 64u * c;
+        const uint32_t mrow0 = m0 + kCR * c;
         const bool in_range = (mrow0 < p.m) && (ncol0 < p.n);  // warp-uniform
         const bool load_c = use_c && in_range;
         if constexpr (kSplitDrain) {
@@ -624,11 +638,11 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (uint32_t t = 0; t < 32; ++t) {
               const uint32_t nj = ncol0 + t;
 #pragma unroll
-              for (uint32_t hh = 0; hh < 2; ++hh) {
+              for (uint32_t hh = 0; hh < kLdPerChunk; ++hh) {
                 const uint32_t i = lane + 32u * hh, mi = mrow0 + i;
                 __half v = __float2half_rn(0.f);
                 if (mi < p.m && nj < p.n) v = c_plain[(size_t)mi + (size_t)nj * p.ldc];
-                hb[t * 64u + ((((i >> 3) ^ (t & 7u)) << 3) | (i & 7u))] = v;
+                hb[t * kCR + ((swz(i >> 3, t) << 3) | (i & 7u))] = v;
               }
             }
             __syncwarp();
@@ -657,15 +671,14 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // with short contractions the epilogue warps are bound by instruction issue.
         auto convert = [&](auto with_c, auto scale) {
           constexpr bool kWithC = decltype(with_c)::value, kScale = decltype(scale)::value;
-          uint8_t* const row = gbuf + lane * 128u;
-          const uint32_t x = lane & 7u;
+          uint8_t* const row = gbuf + lane * (2u * kCR);
 #pragma unroll
-          for (uint32_t h = 0; h < 2; ++h) {
+          for (uint32_t h = 0; h < kLdPerChunk; ++h) {
             const uint32_t(&r)[32] = racc[kEarlyDrain ? 2 * c + h : 2 * kPb + h];
 #pragma unroll
             for (uint32_t jj = 0; jj < 4; ++jj) {
               const uint32_t j = 4u * h + jj;  // 16-byte piece of the 128-byte row
-              uint4* const addr = reinterpret_cast<uint4*>(row + ((j ^ x) << 4));
+              uint4* const addr = reinterpret_cast<uint4*>(row + (swz(j, lane) << 4));
               uint4 out, old;
               uint32_t* po = reinterpret_cast<uint32_t*>(&out);
               if constexpr (kWithC) old = *addr;
@@ -698,9 +711,9 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           __syncwarp();
           if (in_range && ok && (p.diag & 1u) == 0u) {
 #pragma unroll
-            for (uint32_t i = 0; i < 8; ++i) {
-              const uint32_t t = (lane >> 3) + 4u * i, j = lane & 7u;
-              const uint4 v = *reinterpret_cast<const uint4*>(gbuf + t * 128u + ((j ^ (t & 7u)) << 4));
+            for (uint32_t i = 0; i < kRowPieces; ++i) {  // kRowPieces lanes per column, 32 / kRowPieces columns per pass
+              const uint32_t t = lane / kRowPieces + (32u / kRowPieces) * i, j = lane % kRowPieces;
+              const uint4 v = *reinterpret_cast<const uint4*>(gbuf + t * (2u * kCR) + (swz(j, t) << 4));
               const uint32_t row = mrow0 + 8u * j, col = ncol0 + t;
               if (row < p.m && col < p.n) multimem_st_v4(p.c_mc + (size_t)row + (size_t)col * p.ldc, v);
             }
@@ -727,9 +740,9 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (uint32_t t = 0; t < 32; ++t) {
               const uint32_t nj = ncol0 + t;
 #pragma unroll
-              for (uint32_t hh = 0; hh < 2; ++hh) {
+              for (uint32_t hh = 0; hh < kLdPerChunk; ++hh) {
                 const uint32_t i = lane + 32u * hh, mi = mrow0 + i;
-                const __half v = hb[t * 64u + ((((i >> 3) ^ (t & 7u)) << 3) | (i & 7u))];
+                const __half v = hb[t * kCR + ((swz(i >> 3, t) << 3) | (i & 7u))];
                 if (mi < p.m && nj < p.n) c_plain[(size_t)mi + (size_t)nj * p.ldc] = v;
               }
             }

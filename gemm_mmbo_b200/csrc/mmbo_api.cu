@@ -53,6 +53,7 @@ static const KernelRow kF16Rows[] = {
     {"hgemm_tcgen05_MT256x256x64_S3_CG2_WG320_WGM08", 256, 256, 320, 64, 3, 2, 8, 1},
     {"hgemm_tcgen05_MT256x256x64_S5_CG2_WG320_WGM08", 256, 256, 320, 64, 5, 2, 8, 1},
     {"hgemm_tcgen05_MT512x256x64_S4_CG2_WG192_WGM08", 512, 256, 192, 64, 4, 2, 8, 1},
+    {"hgemm_tcgen05_MT512x256x64_S4_CG2_WG320_WGM08", 512, 256, 320, 64, 4, 2, 8, 1},
 };
 // fp64 rows (the reference's own dtype).
 static const KernelRow kF64Rows[] = {
@@ -579,6 +580,9 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   int rc;
   constexpr auto F16 = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   constexpr auto SW = CU_TENSOR_MAP_SWIZZLE_128B;
+  // C goes through staging buffers of kChunkRows rows x 32 columns, swizzled by their row length
+  constexpr uint32_t kCR = HgemmSmem<TM, STAGES, CG, EW, CSETS>::kChunkRows;
+  constexpr auto SWC = kCR == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   // op(A): K-major when transposed (stored k x m), MN-major otherwise (stored m x k).
   if (g.transA)
     rc = make_map(&ta, F16, 2, g.A, g.k, g.m, g.lda, kBlockK, HgemmSmem<TM, STAGES, CG, EW, CSETS>::kPieceRows, SW, g.batch, g.sA);
@@ -594,7 +598,7 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
   // C through TMA only when whole 16-byte units stay inside the matrix (see HgemmParams).
   const bool c_tma = aligned16(g.C) && g.ldc % 8 == 0 && g.m % 8 == 0 && batch_stride_ok(g.batch, g.sC, 2);
   if (c_tma) {
-    rc = make_map(&tc, F16, 2, g.C, g.m, g.n, g.ldc, 64, 32, SW, g.batch, g.sC);
+    rc = make_map(&tc, F16, 2, g.C, g.m, g.n, g.ldc, kCR, 32, SWC, g.batch, g.sC);
     if (rc) return rc;
   } else {
     tc = ta;  // placeholder, never dereferenced by the plain epilogue
@@ -606,7 +610,7 @@ static int launch_hgemm_tcgen05(const GemmArgs& g, uint32_t wgm, cudaStream_t st
     if (!c_tma || g.npeers > kMaxPeerCopies || g.batch != 1) return MMBO_ERR_KERNEL_UNSUITABLE;
     for (int d = 0; d < g.npeers; ++d) {
       if (!g.peers[d] || !aligned16(g.peers[d])) return MMBO_ERR_KERNEL_UNSUITABLE;
-      rc = make_map_2d(&peers.map[d], F16, 2, g.peers[d], g.m, g.n, g.ldc, 64, 32);
+      rc = make_map_2d(&peers.map[d], F16, 2, g.peers[d], g.m, g.n, g.ldc, kCR, 32, SWC);
       if (rc) return rc;
     }
     peers.count = (uint32_t)g.npeers;
@@ -886,18 +890,23 @@ static int select_f16(const GemmArgs& g) {
   const double s3 = 1.00 * eff(t3, sms / 2) * fill(t3, 256, 256);
   // 512-row pair tiles: 25 % less operand staging per flop (8192^3: 1404 against 1358 TFLOP/s; seconds-long loops
   // under the power cap: 1306 against 1257, at a higher clock), but a single accumulator, so the epilogue is
-  // not hidden: only for long contractions.
+  // not hidden: only for long contractions (8192 x 8192 x 4096: 432 against 404 us for the 256-row row; x 8192:
+  // 719-796 against 756-833).
   const uint64_t t6 = nb * ((g.m + 511) / 512) * ((g.n + 255) / 256);
   const double s6 = 1.03 * eff(t6, sms / 2) * fill(t6, 512, 256);
-  if (g.k >= 4096 && s6 >= s3 && s6 >= s1 && s6 >= s2) return 6;
-  // Short contractions are bound by the epilogue: the rows with eight epilogue warps win there.  Up to
-  // k = 512 the one that requests the old C a whole tile ahead into a second set of staging buffers
-  // (three operand stages); up to k = 2048 the one with five stages and an L2 prefetch of the next tile's
-  // C instead (8192 x 8192 x 1024, beta = 1: 131 against 137 us; x 2048: 229 against 248 us; x 512: 92
-  // against 89 us); the six-stage row with four epilogue warps beyond.
-  // Without old C to fetch (beta == 0) the second staging set buys nothing and the five-stage row wins at
-  // every short k (8192 x 8192 x 256: 49.8 against 51.4 us).
-  if (s3 >= s1 && s3 >= s2) return g.k <= 2048 ? ((g.k <= 512 && g.beta != 0.0f) ? 4 : 5) : 3;
+  if (g.k >= 6144 && s6 >= s3 && s6 >= s1 && s6 >= s2) return 6;
+  // Short contractions are bound by the epilogue: the rows with eight epilogue warps win there (measured on
+  // 8192 x 8192 x k, TN, us; rows 4 / 5 / 3):
+  //   beta == 0:  k = 256: 43.6 / 40.4 / 55.5   512: 69.9 / 62.2 / 65.8   1024: 119 / 105.7 / 102.1   2048: 228 / 201 / 190-207
+  //   beta != 0:  k = 256: 59.7 / 62.0 / 99.2   512: 83.7 / 77.1 / 105    1024: 141 / 124.3 / 143.5   2048: 272 / 217 / 206
+  // Row 4 requests the old C a whole tile ahead into a second set of staging buffers (three operand stages): it
+  // pays only while a tile's main loop is shorter than the latency of that request.  Row 5 has five stages and an
+  // L2 prefetch of the next tile's C instead; the six-stage row with four epilogue warps takes over once the main
+  // loop hides the epilogue.
+  if (s3 >= s1 && s3 >= s2) {
+    if (g.beta != 0.0f) return g.k <= 256 ? 4 : (g.k <= 1536 ? 5 : 3);
+    return g.k < 1024 ? 5 : 3;
+  }
   return s1 >= s2 ? 1 : 2;
 }
 
@@ -1134,6 +1143,7 @@ static int run_f16(const GemmArgs& g_in, int id, cudaStream_t st) {
     case 4: rc = launch_hgemm_tcgen05<256, 3, 2, 8>(g, wgm_of(kF16Rows[4]), st); break;
     case 5: rc = launch_hgemm_tcgen05<256, 5, 2, 8, 1>(g, wgm_of(kF16Rows[5]), st); break;
     case 6: rc = launch_hgemm_tcgen05<512, 4, 2, 4>(g, wgm_of(kF16Rows[6]), st); break;
+    case 7: rc = launch_hgemm_tcgen05<512, 4, 2, 8, 1>(g, wgm_of(kF16Rows[7]), st); break;
     default: rc = MMBO_ERR_BAD_KERNEL_ID;
   }
   if (scratch_used) {

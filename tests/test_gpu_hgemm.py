@@ -15,7 +15,7 @@ SHAPES = [(8, 8, 8), (64, 32, 16), (128, 128, 64), (256, 128, 128), (136, 72, 20
           (520, 392, 328), (1024, 512, 640), (40, 1000, 96), (1000, 40, 96)]
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, 5, 6, -1, 0])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, 5, 6, 7, -1, 0])
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_hgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
     for (m, n, k) in SHAPES:
@@ -25,13 +25,13 @@ def test_hgemm_shapes(cuda, mm, oracle, kernel_id, ta, tb):
             run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, 5, 6, -1, 0])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, 5, 6, 7, -1, 0])
 def test_hgemm_beta_zero_never_reads_c(cuda, mm, oracle, kernel_id):
     case = Case(oracle, "f16", False, True, 264, 200, 72, 2.0, 0.0, pad=(0, 8, 16), c_poison=True)
     run_and_check(cuda, mm, case, kernel_id)
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, 5, 6, -1])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, 5, 6, 7, -1])
 def test_hgemm_many_tiles_per_cta(cuda, mm, oracle, kernel_id):
     """More tiles than SMs: every persistent CTA walks several tiles, so stage and
     accumulator phases wrap many times."""
@@ -126,7 +126,7 @@ def _pad_to8(ta, tb, m, n, k, extra=8):
     return tuple((-x) % 8 + extra for x in lead_dims(ta, tb, m, n, k))
 
 
-@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, 5, 6, -1])
+@pytest.mark.parametrize("kernel_id", [1, 2, 3, 4, 5, 6, 7, -1])
 @pytest.mark.parametrize("ta,tb", MODES)
 def test_hgemm_ragged_extents_with_aligned_leading_dims(cuda, mm, oracle, kernel_id, ta, tb):
     """m, n, k that are not multiples of 8 under 8-aligned leading dimensions: the tensor
@@ -151,7 +151,7 @@ def test_hgemm_c_with_odd_leading_dim(cuda, mm, oracle):
         run_and_check(cuda, mm, case, kid)
 
 
-@pytest.mark.parametrize("kernel_id", [-1, 1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("kernel_id", [-1, 1, 2, 3, 4, 5, 6, 7])
 def test_hgemm_result_stored_to_further_copies(cuda, mm, oracle, kernel_id):
     """mmbo_gemm_f16_bcast with the further copies on the same GPU: every copy must hold the same
     bits as C, rows below the matrix untouched; beta != 0 reads the old values from C only."""
