@@ -299,6 +299,19 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t s_bop = smem_base + stage * L::kStageBytes;
           const uint32_t s_aop = s_bop + L::kBopBytes;
           const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
+#if MMBO_TRACE_KB
+          // probe builds: no operand loads after the first fill of the ring (the UMMAs run on what the stages hold;
+          // bit 3 set: no loads at all, the stages stay as they were found)
+          if ((p.diag & 4u) && (issued >= STAGES || (p.diag & 8u))) {
+            if (cta_rank == 0) mbar_arrive(full_bar(stage));
+            ++issued;
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+          }
+#endif
           if (cta_rank == 0) mbar_expect_tx(full_bar(stage), L::kStageBytes * CG);
           auto load = [&](uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1) {
             if constexpr (CG == 2) tma_load_tile_pair(batched, dst, map, bar, c0, c1, prob);
