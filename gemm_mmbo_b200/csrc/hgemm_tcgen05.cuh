@@ -236,19 +236,17 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   };
 
   // ------------------------------------------------------------------ set-up --------
+  static_assert(L::kNumBars <= L::kThreads, "one thread per barrier");
+  if (threadIdx.x < (uint32_t)L::kNumBars) {
+    // one barrier per thread: a single arrival everywhere except on the accumulator-empty barriers, where
+    // every epilogue warp of the CTA (pair) arrives
+    const uint32_t i = threadIdx.x;
+    const bool acc_empty = i >= 2u * STAGES + kAccs && i < 2u * STAGES + 2u * kAccs;
+    mbar_init(bar_base + 8u * i, acc_empty ? EW * CG : 1);
+    fence_mbar_init();
+  }
   if (threadIdx.x == 0) {
     *abort_flag = 0u;
-    for (uint32_t s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (uint32_t a = 0; a < kAccs; ++a) {
-      mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), EW * CG);
-    }
-    for (uint32_t w = 0; w < EW; ++w)
-      for (uint32_t b = 0; b < (uint32_t)L::kBufsPerWarp; ++b) mbar_init(cload_bar(w, b), 1);
-    fence_mbar_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
     if (p.c_tma) prefetch_tensormap(&tmap_c);
@@ -266,6 +264,10 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #if MMBO_TRACE_KB
   if (threadIdx.x == 0) trace_stamp(p.trace, 63u, 1);
 #endif
+  // Set-up is done without touching global memory: the next kernel of the stream may start its own set-up now,
+  // and this one goes on only when the kernel before it has completed (its C may be this one's operand).
+  griddep_launch_dependents();
+  griddep_wait();
 
   // ------------------------------------------------------------------ roles ---------
   if (warp == 0) {
@@ -799,7 +801,8 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       MMBO_ACCT_OUT(8, w_store);
       MMBO_ACCT_OUT(9, w_rel);
     }
-    if (lane == 0) tma_store_wait_all<0>();
+    // Shared memory only has to outlive the stores' reads of it; the end of the grid makes their writes visible.
+    if (lane == 0) tma_store_wait_read<0>();
 #if MMBO_TRACE_KB
     if (warp == 2u && lane == 0u) trace_stamp(p.trace, 63u, 4);
 #endif

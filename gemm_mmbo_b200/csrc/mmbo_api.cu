@@ -132,6 +132,8 @@ struct Settings {
   uint32_t f32_exact;      // MMBO_F32_EXACT: automatic fp32 selection stays on the CUDA-core kernels
   uint32_t dgemm_stage_c;  // MMBO_DGEMM_STAGE_C: 64-row fp64 tiles stage the old C through shared memory
   uint32_t split_k;        // MMBO_SPLIT_K: 0 = automatic, 1 = never split, n > 1 = force n slices where a kernel can
+  uint32_t pdl;            // MMBO_PDL: the persistent tcgen05 kernels are launched with programmatic stream serialization
+                           // (their set-up overlaps the end of the previous kernel of the stream); 0 switches it off
 };
 static Settings load_settings() {
   Settings s;
@@ -142,6 +144,7 @@ static Settings load_settings() {
   s.f32_exact = env_u32("MMBO_F32_EXACT", 0);
   s.dgemm_stage_c = env_u32("MMBO_DGEMM_STAGE_C", 1);
   s.split_k = env_u32("MMBO_SPLIT_K", 0);
+  s.pdl = env_u32("MMBO_PDL", 1);
   return s;
 }
 static Settings& settings() {
@@ -566,10 +569,16 @@ static int launch_hgemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const
   cfg.blockDim = dim3(L::kThreads);
   cfg.dynamicSmemBytes = L::kDynamic;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  // Programmatic dependent launch: the CTAs of this grid may become resident while the previous kernel of the
+  // stream is still finishing; they initialise barriers and tensor memory, then wait (griddepcontrol.wait) for
+  // that kernel to complete and flush before touching global memory.  Every CTA of the grid is resident at once
+  // (persistent grid), so an early start of a dependent grid can never take an SM this grid still needs.
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = settings().pdl ? 2 : 1;
   MMBO_COUNT_LAUNCH();
   return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p, peers);
 }
@@ -720,10 +729,12 @@ static int launch_tf32x3_gemm(const GemmArgs& g, const float* a_hi, const float*
   cfg.blockDim = dim3(L::kThreads);
   cfg.dynamicSmemBytes = L::kDynamic;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // (as for the fp16 kernels)
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = settings().pdl ? 2 : 1;
   MMBO_COUNT_LAUNCH();
   return (int)cudaLaunchKernelEx(&cfg, kern, ta_hi, ta_lo, tb_hi, tb_lo, tc, p);
 }
@@ -1616,6 +1627,7 @@ int mmbo_set_option(const char* name, unsigned int value) {
   else if (!strcmp(name, "f32_exact")) s.f32_exact = value;
   else if (!strcmp(name, "dgemm_stage_c")) s.dgemm_stage_c = value;
   else if (!strcmp(name, "split_k")) s.split_k = value;
+  else if (!strcmp(name, "pdl")) s.pdl = value;
   else return MMBO_ERR_BAD_OPTION;
   return MMBO_OK;
 }
@@ -1630,6 +1642,7 @@ int mmbo_get_option(const char* name, unsigned int* value) {
   else if (!strcmp(name, "f32_exact")) *value = s.f32_exact;
   else if (!strcmp(name, "dgemm_stage_c")) *value = s.dgemm_stage_c;
   else if (!strcmp(name, "split_k")) *value = s.split_k;
+  else if (!strcmp(name, "pdl")) *value = s.pdl;
   else return MMBO_ERR_BAD_OPTION;
   return MMBO_OK;
 }

@@ -195,6 +195,14 @@ __device__ __forceinline__ uint32_t f32x2_to_half2(uint64_t v) {
 }
 
 // ---------------------------------------------------------------- fences -------------
+// Programmatic dependent launch (no-ops in a grid launched without the attribute): let the next kernel of the
+// stream start its set-up; wait until the previous kernel has completed and its writes are visible.
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -199,6 +199,10 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
   }
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
+  // Programmatic dependent launch: set-up done, nothing of global memory touched yet (the split pass that writes
+  // this kernel's operands is the kernel before it in the stream).
+  griddep_launch_dependents();
+  griddep_wait();
 
   // With 8 epilogue warps (384 threads, 168 registers each at launch) the first warpgroup
   // hands registers to the two epilogue warpgroups, whose threads keep 128 running sums:

@@ -222,9 +222,13 @@ const char* mmbo_status_string(int status);
  *   "f32_exact"     non-zero: automatic fp32 selection never takes a split-precision row,
  *                   tuned rows included;
  *   "dgemm_stage_c" 64-row fp64 tiles stage the old C through shared memory (default 1);
- *   "split_k"       0 automatic, 1 never split the contraction, n > 1 force n slices.
+ *   "split_k"       0 automatic, 1 never split the contraction, n > 1 force n slices;
+ *   "pdl"           non-zero (default): the persistent fp16 tensor-core kernels are launched with
+ *                   programmatic stream serialization, so that their set-up overlaps the end of the
+ *                   kernel before them in the stream; they wait for that kernel to complete before
+ *                   they touch global memory, so results and stream order are unchanged.
  * Initial values come from the environment variables MMBO_DIAG, MMBO_WGM, MMBO_TF32_CHUNK,
- * MMBO_F32_EXACT, MMBO_DGEMM_STAGE_C, MMBO_SPLIT_K, which are read once, when the first
+ * MMBO_F32_EXACT, MMBO_DGEMM_STAGE_C, MMBO_SPLIT_K, MMBO_PDL, which are read once, when the first
  * call needs a setting; later changes of the environment have no effect.  (The reference has
  * compile-time #defines only: src/gemm/benchmark.cc:7-14.) */
 int mmbo_set_option(const char* name, unsigned int value);
