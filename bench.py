@@ -357,6 +357,10 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the library has no CPU path")
     torch.cuda.set_device(local_rank)
+    host_affinity = None
+    if world > 1:  # several ranks share the host: keep each one's pinned buffers on its GPU's NUMA node
+        from gemm_mmbo_b200.sharded import bind_host_to_device
+        host_affinity = bind_host_to_device(local_rank)
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -579,7 +583,8 @@ def main():
             "scaling": "strong" if P > 1 else "weak", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic",
             "config": {"workload": w["name"], "m": m, "n": n, "k": k, "columns_per_gpu": ncols,
-                       "gather_c": False, "l2": "inputs larger than L2 (126 MB)", "accumulate": "fp32"},
+                       "gather_c": False, "l2": "inputs larger than L2 (126 MB)", "accumulate": "fp32",
+                       "host_affinity_rank0": host_affinity},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "rel_err": rel_err,
             "per_rank": per_rank, "vendor": vendor, "exchange": exchange, **extras,
             "cpu_baseline": cpu, "impl": "ours",
@@ -606,6 +611,11 @@ def exchange_legs(torch, dist, mm, O, w, args, rank, P, col0, ncols, A, B, ra, r
     def leg(name, fn, Cfull, note):
         ok = torch.ones(1, device="cuda")
         try:
+            # The same GEMM without the exchange, into the same buffer, timed right before the leg: under the power
+            # cap the clock of a long run drifts, so a ratio against a figure taken minutes earlier says little.
+            own = Cfull[col0:col0 + ncols]
+            near_ms, _ = timed(lambda: mm.gemm("f16", ta, tb, m, ncols, k, w["alpha"], A, ra, B, rb, w["beta"], own, m,
+                                               args.kernel), steps, 2)
             ms, _ = timed(fn, steps, 2)
             Cfull.fill_(float("nan"))
             barrier()
@@ -614,7 +624,8 @@ def exchange_legs(torch, dist, mm, O, w, args, rank, P, col0, ncols, A, B, ra, r
             err = sampled_rel_err(O, w, lambda r, c: Cfull[torch.as_tensor(c), torch.as_tensor(r)].double().cpu().numpy(),
                                   peer_c0, peer_c0 + peer_nc, nsamp=24, seed=100 + rank)
             finite = bool(torch.isfinite(Cfull).all().item())
-            res = {"ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "x_no_exchange": ms / base_ms,
+            res = {"ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "no_exchange_ms_just_before": near_ms,
+                   "x_no_exchange": ms / near_ms, "x_first_timed_region": ms / base_ms,
                    "rel_err": err, "whole_c_finite": finite, "how": note}
         except Exception as e:  # a rank that cannot run a leg says so; the others learn it below
             ok.zero_()

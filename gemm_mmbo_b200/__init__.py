@@ -18,10 +18,18 @@ _PUBLIC = (
 __all__ = list(_PUBLIC)
 
 
+def _bind_public():
+    """Bind the public names to the functions of the `gemm` submodule.  Importing that submodule makes Python set
+    the package attribute `gemm` to the MODULE, which would hide the function of the same name; every internal
+    importer of the submodule calls this afterwards, so `gemm_mmbo_b200.gemm(...)` works whatever was imported first."""
+    mod = importlib.import_module(__name__ + ".gemm")  # loads libmmbo_gemm.so or raises
+    for n in _PUBLIC:
+        globals()[n] = getattr(mod, n)
+    return mod
+
+
 def __getattr__(name):
     if name in _PUBLIC:
-        mod = importlib.import_module(__name__ + ".gemm")  # loads libmmbo_gemm.so or raises
-        for n in _PUBLIC:
-            globals()[n] = getattr(mod, n)
+        _bind_public()
         return globals()[name]
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

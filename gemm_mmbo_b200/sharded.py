@@ -18,8 +18,8 @@ from __future__ import annotations
 import importlib
 from dataclasses import dataclass
 
-# the package re-exports a function called `gemm`, which hides the submodule attribute
-_g = importlib.import_module(__package__ + ".gemm")
+# the package re-exports a function called `gemm`; importing the submodule of that name must not hide it
+_g = importlib.import_module(__package__)._bind_public()
 
 
 @dataclass(frozen=True)
@@ -154,6 +154,32 @@ class ColumnShard:
             comm = nccl_comm_ptr()
         _g.gemm_sharded_host(self.world, self.rank, comm, transA, transB, m, self.n, k, alpha, hA, lda, hB_block, ldb,
                              beta, hC_block, ldc, kernelId)
+
+
+def bind_host_to_device(device_index: int) -> str:
+    """Run this process on the CPU cores next to GPU `device_index` (NVML's ideal affinity for the device,
+    intersected with the cores the process may use), so that pinned host buffers allocated afterwards live on
+    that GPU's NUMA node and host <-> device copies of several ranks do not all cross the same socket link.
+    Only this process's own CPU affinity changes; nothing of the GPU is touched.  Returns a short description
+    of what was done (for a benchmark record); never raises."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        ideal = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        pick = ideal & allowed
+        if not pick:
+            return "unchanged (no allowed core in the device's ideal set)"
+        if pick == allowed:
+            return f"unchanged (all {len(allowed)} allowed cores are local)"
+        os.sched_setaffinity(0, pick)
+        return f"{len(pick)} of {len(allowed)} allowed cores (local to GPU {device_index})"
+    except Exception as e:  # no NVML, no affinity support: run where the launcher put us
+        return f"unchanged ({type(e).__name__})"
 
 
 def nccl_comm_ptr(group=None) -> int:

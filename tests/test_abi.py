@@ -220,3 +220,15 @@ def test_shares_of_a_tile_its_columns_on_16_byte_boundaries(mm, cols, world):
         assert c0 == pos and c0 % 8 == 0
         pos += cn
     assert pos == cols
+
+
+def test_public_names_survive_any_import_order():
+    """`gemm_mmbo_b200.gemm` is a function even when a submodule that needs the binding (`sharded`) was imported
+    first -- Python would otherwise bind the package attribute to the submodule of the same name."""
+    import subprocess
+    import sys
+    code = ("import gemm_mmbo_b200 as mm\n"
+            "from gemm_mmbo_b200.sharded import ColumnShard\n"
+            "assert callable(mm.gemm) and callable(mm.gemm_host) and callable(mm.select_kernel), type(mm.gemm)\n")
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(ROOT))
+    assert res.returncode == 0, res.stderr
