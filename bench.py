@@ -607,15 +607,23 @@ def exchange_legs(torch, dist, mm, O, w, args, rank, P, col0, ncols, A, B, ra, r
     flops = 2.0 * m * n * k
     peer_c0, peer_nc = shard.block_of((rank + 1) % P)
     out = {"steps": steps, "no_exchange_ms_per_step": base_ms}
+    token = torch.zeros(1, device="cuda")  # a one-element all-reduce: the stream-ordered meeting point of the NCCL leg
 
-    def leg(name, fn, Cfull, note):
+    def leg(name, fn, Cfull, note, sync):
         ok = torch.ones(1, device="cuda")
         try:
             # The same GEMM without the exchange, into the same buffer, timed right before the leg: under the power
             # cap the clock of a long run drifts, so a ratio against a figure taken minutes earlier says little.
             own = Cfull[col0:col0 + ncols]
-            near_ms, _ = timed(lambda: mm.gemm("f16", ta, tb, m, ncols, k, w["alpha"], A, ra, B, rb, w["beta"], own, m,
-                                               args.kernel), steps, 2)
+
+            def plain():
+                mm.gemm("f16", ta, tb, m, ncols, k, w["alpha"], A, ra, B, rb, w["beta"], own, m, args.kernel)
+
+            def plain_lockstep():  # ... and with the ranks meeting after every step, as every exchange makes them do
+                plain()
+                sync()
+            near_ms, _ = timed(plain, steps, 2)
+            lock_ms, _ = timed(plain_lockstep, steps, 2)
             ms, _ = timed(fn, steps, 2)
             Cfull.fill_(float("nan"))
             barrier()
@@ -625,7 +633,8 @@ def exchange_legs(torch, dist, mm, O, w, args, rank, P, col0, ncols, A, B, ra, r
                                   peer_c0, peer_c0 + peer_nc, nsamp=24, seed=100 + rank)
             finite = bool(torch.isfinite(Cfull).all().item())
             res = {"ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "no_exchange_ms_just_before": near_ms,
-                   "x_no_exchange": ms / near_ms, "x_first_timed_region": ms / base_ms,
+                   "no_exchange_lockstep_ms_just_before": lock_ms,
+                   "x_no_exchange": ms / near_ms, "x_no_exchange_lockstep": ms / lock_ms, "x_first_timed_region": ms / base_ms,
                    "rel_err": err, "whole_c_finite": finite, "how": note}
         except Exception as e:  # a rank that cannot run a leg says so; the others learn it below
             ok.zero_()
@@ -650,12 +659,13 @@ def exchange_legs(torch, dist, mm, O, w, args, rank, P, col0, ncols, A, B, ra, r
             leg("fused_multicast",
                 lambda: shard.gemm_and_multicast(ta, tb, m, k, w["alpha"], A, ra, B, rb, w["beta"], Csym, kernelId=args.kernel),
                 Csym.tensor, "mmbo_gemm_f16_mcast: epilogue writes each piece once with multimem.st, NVSwitch "
-                             "delivers it to every GPU; stream-ordered barrier ends the step")
+                             "delivers it to every GPU; stream-ordered barrier ends the step", Csym.barrier)
         else:
             out["fused_multicast"] = {"error": "no NVLink multicast mapping on this system"}
         leg("fused_peer_stores",
             lambda: shard.gemm_and_broadcast(ta, tb, m, k, w["alpha"], A, ra, B, rb, w["beta"], Csym, kernelId=args.kernel),
-            Csym.tensor, "mmbo_gemm_f16_bcast: epilogue issues one TMA store per GPU for each piece; barrier ends the step")
+            Csym.tensor, "mmbo_gemm_f16_bcast: epilogue issues one TMA store per GPU for each piece; barrier ends the step",
+            Csym.barrier)
     barrier()
     Cfull = Csym.tensor if Csym is not None else torch.empty((n, m), dtype=torch.float16, device="cuda")
     comm = None
@@ -666,7 +676,8 @@ def exchange_legs(torch, dist, mm, O, w, args, rank, P, col0, ncols, A, B, ra, r
     if comm is not None:
         leg("nccl_all_gather",
             lambda: shard.gemm_sharded(ta, tb, m, k, w["alpha"], A, ra, B, rb, w["beta"], Cfull, True, comm, args.kernel),
-            Cfull, "mmbo_gemm_f16_sharded(gatherC=1): GEMM, then ncclAllGather in place on the same stream")
+            Cfull, "mmbo_gemm_f16_sharded(gatherC=1): GEMM, then ncclAllGather in place on the same stream",
+            lambda: dist.all_reduce(token))
     barrier()
     # every rank leaves the multicast object together, with nothing in flight
     del Cfull
