@@ -11,7 +11,7 @@ import importlib
 
 _PUBLIC = (
     "DTYPE_F16", "DTYPE_F32", "DTYPE_F64", "dgemm_NN", "dgemm_NT", "dgemm_TN", "dgemm_TT", "KERNEL_AUTO", "DIST_UNIFORM", "DIST_NORMAL", "DIST_ZERO", "MAT_A", "MAT_B",
-    "MAT_C", "MmboError", "device_status", "fill", "gemm", "gemm_bcast", "gemm_mcast", "gemm_sharded", "gemm_sharded_host", "gemm_host", "set_option", "get_option", "launch_count", "gemm_strided_batched", "hgemm_NN", "hgemm_NT", "hgemm_TN", "hgemm_TT",
+    "MAT_C", "MmboError", "device_status", "fill", "gemm", "gemm_bcast", "gemm_mcast", "gemm_sharded", "gemm_sharded_host", "gemm_host", "set_option", "get_option", "launch_count", "last_kernel", "gemm_strided_batched", "hgemm_NN", "hgemm_NT", "hgemm_TN", "hgemm_TT",
     "kernel_name", "kernel_params", "kernel_table", "num_kernels", "select_kernel", "sgemm_NN", "sgemm_NT",
     "sgemm_TN", "sgemm_TT", "shard_columns", "status_string", "wgm_map", "workspace_bytes", "set_workspace", "tuning_set", "tuning_load", "tuning_clear",
 )

@@ -70,6 +70,7 @@ SIGNATURES = {
     "mmbo_set_option": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_uint]),
     "mmbo_get_option": (ctypes.c_int, [ctypes.c_char_p, _u32p]),
     "mmbo_launch_count": (ctypes.c_ulonglong, []),
+    "mmbo_last_kernel": (ctypes.c_int, [ctypes.c_int]),
     "mmbo_gemm_f32_noalloc": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _sz, _sz, _sz, _fp, _vp, _sz, _vp, _sz,
                                              _fp, _vp, _sz, _vp]),
 }

@@ -933,7 +933,10 @@ static int select_f32_fitting(const GemmArgs& g) {
   return id;
 }
 
+static int g_last_kernel[3] = {-1, -1, -1};  // row the last call of each dtype ran (mmbo_last_kernel)
+
 static int run_f32(const GemmArgs& g, int id, cudaStream_t st) {
+  g_last_kernel[MMBO_DTYPE_F32] = id;
   if (g.m == 0 || g.n == 0) return MMBO_OK;
   if (g.k == 0) return launch_scale<float>(g, st);
   switch (id) {
@@ -982,6 +985,7 @@ static int select_f64(const GemmArgs& g) {
 }
 
 static int run_f64(const GemmArgs& g, double alpha, double beta, int id, cudaStream_t st) {
+  g_last_kernel[MMBO_DTYPE_F64] = id;
   if (g.m == 0 || g.n == 0) return MMBO_OK;
   const double* A = static_cast<const double*>(g.A);
   const double* B = static_cast<const double*>(g.B);
@@ -1139,6 +1143,7 @@ static int realign_f16(GemmArgs& g, cudaStream_t st, bool* scratch_used) {
 }
 
 static int run_f16(const GemmArgs& g_in, int id, cudaStream_t st) {
+  g_last_kernel[MMBO_DTYPE_F16] = id;
   if (g_in.m == 0 || g_in.n == 0) return MMBO_OK;
   if (g_in.k == 0) return launch_scale<__half>(g_in, st);
   if (id == 0) return launch_simple<__half>(g_in, st);
@@ -1615,6 +1620,12 @@ int mmbo_gemm_strided_batched(int dtype, int transA, int transB, size_t m, size_
 unsigned long long mmbo_launch_count(void) {
   MMBO_API_LOCK();
   return g_launch_count;
+}
+
+int mmbo_last_kernel(int dtype) {
+  MMBO_API_LOCK();
+  if (dtype != MMBO_DTYPE_F32 && dtype != MMBO_DTYPE_F16 && dtype != MMBO_DTYPE_F64) return MMBO_ERR_BAD_DTYPE;
+  return g_last_kernel[dtype];
 }
 
 int mmbo_set_option(const char* name, unsigned int value) {

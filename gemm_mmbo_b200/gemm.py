@@ -296,3 +296,8 @@ def get_option(name: str) -> int:
 def launch_count() -> int:
     """Kernel launches the library has queued since it was loaded."""
     return int(LIB.mmbo_launch_count())
+
+
+def last_kernel(dtype) -> int:
+    """Table row the most recent GEMM call of `dtype` ran (-1 before the first)."""
+    return int(LIB.mmbo_last_kernel(_DTYPES[dtype]))

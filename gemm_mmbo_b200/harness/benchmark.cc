@@ -138,11 +138,10 @@ int main(int argc, char** argv) {
 
   if (o.type == 0) {
     int id = o.kernel;
-    if (id == MMBO_KERNEL_AUTO)
-      id = mmbo_select_kernel(o.dtype, o.transA, o.transB, o.M, o.N, o.K, dA, o.lda, dB, o.ldb, dC, o.ldc);
-    MMBO_CHECK(id < 0 ? id : 0);
     double tflops = 0;
     MMBO_CHECK(time_kernel(id, &tflops));
+    if (id == MMBO_KERNEL_AUTO) id = mmbo_last_kernel(o.dtype);  // the row the library chose for these arguments, beta included
+    MMBO_CHECK(id < 0 ? id : 0);
     std::printf("%s\n", mmbo_kernel_name(o.dtype, id));
     std::printf("mmbo_%sgemm(%s): kernel, m, n, k, lda, ldb, time, tflops, efficiency = %d, %zu, %zu, %zu, %zu, "
                 "%zu, %.6f, %.5f, %.2f%%\n", prefix, trans, id, o.M, o.N, o.K, o.lda, o.ldb, seconds, tflops,

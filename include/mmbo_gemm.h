@@ -240,6 +240,12 @@ int mmbo_get_option(const char* name, unsigned int* value);
  * src/gemm/driver.h:56-59). */
 unsigned long long mmbo_launch_count(void);
 
+/* Table row that the most recent GEMM call of `dtype` in this process ran (the row an automatic
+ * selection resolved to -- it depends on beta, which mmbo_select_kernel does not see), -1 before
+ * the first call; MMBO_ERR_BAD_DTYPE for an unknown dtype.  The reference prints the kernel it
+ * picked from its own table: src/gemm/benchmark.cc:92-106. */
+int mmbo_last_kernel(int dtype);
+
 /* Tile rasterisation used by the kernels (the reference's work-group mapping,
  * src/gemm/ref/Kernels.cpp:209-236), exposed for host-side checks. */
 void mmbo_wgm_map(uint32_t wg0, uint32_t wg1, uint32_t nwg0, uint32_t nwg1, uint32_t wgm,

@@ -186,3 +186,25 @@ def test_hgemm_bcast_refuses_what_tma_cannot_store(cuda, mm, oracle):
     assert e.value.status == -8  # MMBO_ERR_KERNEL_UNSUITABLE
     with pytest.raises(mm.MmboError):
         mm.gemm_bcast(False, True, 256, n, k, 1.0, A, 256, B, n, 0.0, C, 256, [C] * 8)  # more than 7 copies
+
+
+@pytest.mark.gpu
+def test_last_kernel_reports_the_row_an_automatic_call_ran(cuda, mm, oracle):
+    """Automatic selection depends on beta (short contractions: the row that requests old C a tile ahead only pays
+    when there is old C), which `select_kernel` cannot see; `last_kernel` names the row that actually ran."""
+    import torch
+    m = n = 4096
+    k = 256
+    A = (torch.randn((m, k), device="cuda") * 0.5).half()   # TN: A stored k x m, B stored k x n
+    B = (torch.randn((n, k), device="cuda") * 0.5).half()
+    C = torch.zeros((n, m), dtype=torch.float16, device="cuda")
+    mm.gemm("f16", True, False, m, n, k, 1.0, A, k, B, k, 0.0, C, m)
+    no_c = mm.last_kernel("f16")
+    mm.gemm("f16", True, False, m, n, k, 1.0, A, k, B, k, 1.0, C, m)
+    with_c = mm.last_kernel("f16")
+    mm.gemm("f16", True, False, m, n, k, 1.0, A, k, B, k, 1.0, C, m, 3)
+    forced = mm.last_kernel("f16")
+    torch.cuda.synchronize()
+    names = [mm.kernel_name("f16", i) for i in (no_c, with_c)]
+    assert forced == 3
+    assert "S5_CG2_WG320" in names[0] and "S3_CG2_WG320" in names[1], names
