@@ -560,13 +560,11 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       };
       // With at most 128 accumulator columns per warp the whole share is pulled into registers (no
-      // register buffer is reused within a tile) and the accumulator handed back at once.  Tensor-memory
-      // loads are slow -- about ten cycles per register and warp, and the warps of one scheduler share
-      // its port (measured: 1340 cycles for 128 columns, with or without UMMAs running).
+      // register buffer is reused within a tile) and the accumulator handed back at once: a 32-column
+      // tensor-memory load takes about 17 cycles once the loads are pipelined (86 cycles for 128 columns; the
+      // two warps of a scheduler share its port), so the hand-back comes a few hundred cycles after the
+      // accumulator is complete and the issuer can start the tile after next.
       constexpr bool kEarlyDrain = kChunksPerWarp <= 2;
-      // (Measured on 44160 x 2048 x 384: 121 us with the split against 106 us without: the loads of the second
-      // half do not progress while the warp works on the first, so the switch stays off.)
-      constexpr bool kSplitDrain = false;
       // Otherwise two register buffers of one chunk each: the tensor-memory loads of chunk
       // c + 1 are in flight while chunk c is scaled, converted and staged.
       uint32_t racc[kEarlyDrain ? 2 * kChunksPerWarp : 4][32];
@@ -588,21 +586,13 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int e = 0; e < 32; ++e) racc[i][e] = 0u;
           }
         };
-        if constexpr (kSplitDrain) {
-          load_piece(0);
-          load_piece(1);
-          tmem_ld_wait();
-          load_piece(2);  // in flight during chunk 0; awaited, and the accumulator released, before chunk 1
-          load_piece(3);
-        } else {
+        {
+          MMBO_ACCT_BEGIN();
 #pragma unroll
-          {
-            MMBO_ACCT_BEGIN();
-            for (uint32_t i = 0; i < 2 * kChunksPerWarp; ++i) load_piece(i);
-            tmem_ld_wait();
-            release_accumulator();
-            MMBO_ACCT_END(w_rel);
-          }
+          for (uint32_t i = 0; i < 2 * kChunksPerWarp; ++i) load_piece(i);
+          tmem_ld_wait();
+          release_accumulator();
+          MMBO_ACCT_END(w_rel);
         }
         if (tracer) trace_stamp(p.trace, local_tile, 3);
         if (kCAhead && c_tma && use_c && tile + kAhead * num_walkers < num_tiles) {
@@ -622,12 +612,6 @@ hgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t mrow0 = m0 + kCR * c;
         const bool in_range = (mrow0 < p.m) && (ncol0 < p.n);  // warp-uniform
         const bool load_c = use_c && in_range;
-        if constexpr (kSplitDrain) {
-          if (c == 1u) {  // the second half of the accumulator is in registers now: hand it back
-            tmem_ld_wait();
-            release_accumulator();
-          }
-        }
         if (c_tma) {
           if (!use_c || c >= 2u) {
             // The store last issued from this buffer (kStoresPending + 1 chunks ago) must have read it.
