@@ -94,12 +94,25 @@ def main() -> None:
                     results.append((2.0 * m * n * k / ms / 1e9, kid, split))
         results.sort(reverse=True)
         best = results[0]
-        # a row is written only where measurement beats the built-in heuristic by more than 2 %
+        # a row is written only where another row (or split mode) beats the built-in heuristic's choice
         ta, tb = trans[0] == "T", trans[1] == "T"
         heur = mm.select_kernel(dtype, ta, tb, m, n, k, 4096, (k if ta else m), 4096, (n if tb else k), 4096, m)
         heur_ms = time_kernel(mm, torch, dtype, trans, m, n, k, heur, args.iters, 0)  # the library's own split decision
         heur_tf = 2.0 * m * n * k / heur_ms / 1e9 if heur_ms else 0.0
-        if best[0] > 1.02 * heur_tf:
+        better = False
+        if (best[1], best[2]) != (heur, 0) and best[0] > 1.02 * heur_tf:
+            # confirm with two more interleaved measurements of each (clocks drift under the power cap): the row is
+            # written only when the candidate's best beats the heuristic's best by more than 3 %
+            cand, base = [best[0]], [heur_tf]
+            for _ in range(2):
+                ms = time_kernel(mm, torch, dtype, trans, m, n, k, best[1], args.iters, best[2])
+                cand.append(2.0 * m * n * k / ms / 1e9 if ms else 0.0)
+                ms = time_kernel(mm, torch, dtype, trans, m, n, k, heur, args.iters, 0)
+                base.append(2.0 * m * n * k / ms / 1e9 if ms else 0.0)
+            best = (max(cand), best[1], best[2])
+            heur_tf = max(base)
+            better = best[0] > 1.03 * heur_tf
+        if better:
             split = f" {best[2]}" if best[2] else ""
             lines.append(f"{dtype} {trans} {m} {n} {k} {best[1]}{split}   # {best[0]:.1f} (heuristic {heur}: {heur_tf:.1f})")
         else:

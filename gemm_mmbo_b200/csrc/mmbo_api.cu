@@ -867,9 +867,10 @@ static int select_f32(const GemmArgs& g) {
   const double work = (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
   if (work >= 512.0 * 512.0 * 512.0 && !exact) {
     const uint64_t big_pairs = (uint64_t)((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch;
-    // 256 x 256 pair tiles from 32 of them on (measured by the autotuner: 2048^3 173 against 134 TFLOP/s for the
-    // 128 x 256 row, 2368^3 148 / 135, 3072^3 231 / 178, 1536 x 2048 x 384 73 / 63)
-    if (big_pairs >= 32) return 5;
+    // 256 x 256 pair tiles from 48 of them on (measured by the autotuner: 2048^3 173 against 134 TFLOP/s for the
+    // 128 x 256 row, 2368^3 148 / 135, 3072^3 231 / 178, 1536 x 2048 x 384 (48 tiles) 73 / 63; but 1536^3 (36 tiles)
+    // 105 against 133 for the 128 x 128 row)
+    if (big_pairs >= 48) return 5;
     const uint64_t pair_tiles = (uint64_t)((g.m + 127) / 128) * ((g.n + 255) / 256) * g.batch;
     return pair_tiles >= (uint64_t)(sm_count() / 2) ? 3 : 4;
   }
@@ -915,6 +916,9 @@ static int select_f16(const GemmArgs& g) {
   // L2 prefetch of the next tile's C instead; the six-stage row with four epilogue warps takes over once the main
   // loop hides the epilogue.
   if (s3 >= s1 && s3 >= s2) {
+    // At most two tiles per CTA pair: the last epilogue is not hidden behind anything, and eight epilogue warps
+    // finish it sooner (autotuner, beta = 0.5: 2048^3 874 against 798 TFLOP/s, 2368^3 783 against 753).
+    if (t3 <= 2 * (uint64_t)(sms / 2) && g.k <= 4096) return (g.k <= 256 && g.beta != 0.0f) ? 4 : 5;
     if (g.beta != 0.0f) return g.k <= 256 ? 4 : (g.k <= 1536 ? 5 : 3);
     return g.k < 1024 ? 5 : 3;
   }
