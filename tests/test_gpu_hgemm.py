@@ -208,3 +208,38 @@ def test_last_kernel_reports_the_row_an_automatic_call_ran(cuda, mm, oracle):
     names = [mm.kernel_name("f16", i) for i in (no_c, with_c)]
     assert forced == 3
     assert "S5_CG2_WG320" in names[0] and "S3_CG2_WG320" in names[1], names
+
+
+@pytest.mark.parametrize("kernel_id", [2, 3, 5, 6])
+def test_hgemm_chain_on_one_stream_sees_the_previous_result(cuda, mm, oracle, kernel_id):
+    """Back-to-back launches overlap their set-up with the end of the kernel before them (programmatic dependent
+    launch): a GEMM whose operand is the C of the GEMM queued just before it on the same stream must still read the
+    finished C.  Ten chained pairs, each compared bitwise with the same pair run with a synchronize in between and
+    with the overlap switched off."""
+    torch = cuda
+    m = n = k = 512
+    gen = torch.Generator(device="cuda").manual_seed(7 + kernel_id)
+    A = (torch.randn((k, m), device="cuda", generator=gen) * 0.25).half()
+    B = (torch.randn((n, k), device="cuda", generator=gen) * 0.25).half()
+    B2 = (torch.randn((n, m), device="cuda", generator=gen) * 0.25).half()
+
+    def pair(sync_between):
+        C1 = torch.full((n, m), float("nan"), dtype=torch.float16, device="cuda")
+        C2 = torch.full((n, m), float("nan"), dtype=torch.float16, device="cuda")
+        mm.gemm("f16", False, False, m, n, k, 1.0, A, m, B, k, 0.0, C1, m, kernel_id)
+        if sync_between:
+            torch.cuda.synchronize()
+        mm.gemm("f16", False, False, m, n, n, 1.0, C1, m, B2, n, 0.0, C2, m, kernel_id)  # op(A) of the second = C of the first
+        torch.cuda.synchronize()
+        return C2.cpu().numpy().view(np.uint16)
+
+    assert mm.get_option("pdl") == 1
+    try:
+        mm.set_option("pdl", 0)
+        want = pair(True)
+        mm.set_option("pdl", 1)
+        assert np.isfinite(want.view(np.float16)).all()
+        for _ in range(10):
+            assert np.array_equal(pair(False), want)
+    finally:
+        mm.set_option("pdl", 1)
