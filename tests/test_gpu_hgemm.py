@@ -233,7 +233,7 @@ def test_hgemm_chain_on_one_stream_sees_the_previous_result(cuda, mm, oracle, ke
         torch.cuda.synchronize()
         return C2.cpu().numpy().view(np.uint16)
 
-    assert mm.get_option("pdl") == 1
+    before = mm.get_option("pdl")
     try:
         mm.set_option("pdl", 0)
         want = pair(True)
@@ -242,4 +242,4 @@ def test_hgemm_chain_on_one_stream_sees_the_previous_result(cuda, mm, oracle, ke
         for _ in range(10):
             assert np.array_equal(pair(False), want)
     finally:
-        mm.set_option("pdl", 1)
+        mm.set_option("pdl", before)
